@@ -151,7 +151,7 @@ def randomize_pages(runner, torch) -> None:
     g = torch.Generator(device=runner.device)
     g.manual_seed(1)
     for s, t in runner.cache.storage.items():
-        if t.dim() == 5:
+        if not isinstance(t, list) and t.dim() == 5:
             flat = t.view(-1)
             step = 1 << 28
             for i in range(0, flat.numel(), step):

@@ -21,7 +21,7 @@ import math
 
 import torch
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import FixedState, PagedKV, StateBundle
 
 
 class PagedKVView:
@@ -73,6 +73,18 @@ class FixedStateKind:
 
     def view(self, storage, writes, need):
         return FixedStateView(storage, writes)
+
+
+def flatten_need(need) -> list:
+    """The plain needs behind one cache slot: a bundle's parts in order, a single need as a list of one, none as []."""
+    if need is None:
+        return []
+    if isinstance(need, StateBundle):
+        out = []
+        for part in need.parts:
+            out += flatten_need(part)
+        return out
+    return [need]
 
 
 _KINDS: dict = {}

@@ -27,7 +27,8 @@ import ctypes
 import numpy as np
 import torch
 
-from .kinds import FixedStateView, PagedKVView, kind_of       # the views are re-exported from here
+from ..parts.base import StateBundle
+from .kinds import FixedStateView, PagedKVView, flatten_need, kind_of       # the views are re-exported from here
 
 _OK, _E_NOT_LIVE, _E_ALREADY_LIVE, _E_NO_SLOT, _E_OUT_OF_PAGES, _E_CONTEXT, _E_COMMIT, _E_PAGE, _E_INCONSISTENT = range(9)
 
@@ -171,35 +172,44 @@ class CacheManager:
         self.max_pages_per_request = -(-self.max_context // self.page_size)
         self.dtype, self.device = dtype, torch.device(device)
         self.needs = list(needs)
-        self._kinds = [None if n is None else kind_of(n) for n in self.needs]
+        # a cache slot holds one state, or several (a bundle): `_units[s]` lists (need, kind, storage) of each part, and
+        # `storage[s]` is the part's tensor, or the list of them for a bundle
+        self._units: list[list] = [[] for _ in self.needs]
         self._lib = host_library()
         self.groups: list[_Group] = []
         self._group_of_slot: dict[int, int] = {}
-        self.storage: dict[int, torch.Tensor] = {}
+        self.storage: dict = {}
         by_window: dict = {}
         pool_sizes: list[int] = []
-        for s, (need, kind) in enumerate(zip(self.needs, self._kinds)):
-            if need is None:
-                continue
-            if kind.paged:
-                window = kind.window(need)
-                g = by_window.get(window)
-                if g is None:
-                    if isinstance(n_pages, dict):
-                        n = n_pages[window]
-                    else:
-                        n = n_pages_windowed if (window is not None and n_pages_windowed is not None) else n_pages
-                    g = len(self.groups)
-                    by_window[window] = g
-                    self.groups.append(_Group(self, g, window, int(n)))
-                    pool_sizes.append(int(n))
-                self.groups[g].slots.append(s)
-                self._group_of_slot[s] = g
-                self.storage[s] = torch.zeros((pool_sizes[g], *kind.page_shape(need, self.page_size)),
-                                              dtype=kind.dtype(need, dtype), device=self.device)
-            else:
-                self.storage[s] = torch.zeros((self.max_requests, *kind.shape(need)), dtype=kind.dtype(need, dtype),
-                                              device=self.device)
+        for s, whole in enumerate(self.needs):
+            for need in flatten_need(whole):
+                kind = kind_of(need)
+                if kind.paged:
+                    window = kind.window(need)
+                    g = by_window.get(window)
+                    if g is None:
+                        if isinstance(n_pages, dict):
+                            n = n_pages[window]
+                        else:
+                            n = n_pages_windowed if (window is not None and n_pages_windowed is not None) else n_pages
+                        g = len(self.groups)
+                        by_window[window] = g
+                        self.groups.append(_Group(self, g, window, int(n)))
+                        pool_sizes.append(int(n))
+                    if s in self._group_of_slot and self._group_of_slot[s] != g:
+                        raise ValueError(f"cache slot {s}: the paged parts of a bundle must share one window")
+                    if s not in self.groups[g].slots:
+                        self.groups[g].slots.append(s)
+                    self._group_of_slot[s] = g
+                    store = torch.zeros((pool_sizes[g], *kind.page_shape(need, self.page_size)),
+                                        dtype=kind.dtype(need, dtype), device=self.device)
+                else:
+                    store = torch.zeros((self.max_requests, *kind.shape(need)), dtype=kind.dtype(need, dtype),
+                                        device=self.device)
+                self._units[s].append((need, kind, store))
+            if self._units[s]:
+                stores = [u[2] for u in self._units[s]]
+                self.storage[s] = stores if isinstance(whole, StateBundle) else stores[0]
         G = len(self.groups)
         windows = (ctypes.c_int * max(G, 1))(*[(-1 if g.window is None else int(g.window)) for g in self.groups])
         sizes = (ctypes.c_int * max(G, 1))(*pool_sizes)
@@ -268,9 +278,10 @@ class CacheManager:
         self._zero_fixed(slot)
 
     def _zero_fixed(self, slot: int) -> None:
-        for s, kind in enumerate(self._kinds):
-            if kind is not None and not kind.paged:
-                self.storage[s][slot].zero_()
+        for units in self._units:
+            for _need, kind, store in units:
+                if not kind.paged:
+                    store[slot].zero_()
 
     def forget(self, request) -> None:
         """The native side has released `request` (finished or preempted): drop it here."""
@@ -330,12 +341,13 @@ class CacheManager:
         return self._group_of_slot.get(cache_slot)
 
     def view(self, cache_slot: int, writes: bool):
-        need, kind = self.needs[cache_slot], self._kinds[cache_slot]
-        if kind is None:
+        """What the mixer of `cache_slot` is handed: the view of its state, a tuple of views for a bundle, or None."""
+        units = self._units[cache_slot]
+        if not units:
             return None
-        if kind.paged:
-            return kind.view(self.storage[cache_slot], self.page_size, self._group_of_slot[cache_slot], writes, need)
-        return kind.view(self.storage[cache_slot], writes, need)
+        views = tuple(kind.view(store, self.page_size, self._group_of_slot[cache_slot], writes, need) if kind.paged
+                      else kind.view(store, writes, need) for need, kind, store in units)
+        return views if isinstance(self.needs[cache_slot], StateBundle) else views[0]
 
     # ---- accounting and self-check -----------------------------------------------------------------------
     def free_pages(self) -> list[int]:
@@ -349,13 +361,18 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Bytes one token adds over all paged cache slots (windowed slots included, as long as it is in reach)."""
         n = 0
-        for s, (need, kind) in enumerate(zip(self.needs, self._kinds)):
-            if kind is not None and kind.paged:
-                n += kind.page_bytes(need, self.page_size, self.storage[s].element_size()) // self.page_size
+        for units in self._units:
+            for need, kind, store in units:
+                if kind.paged:
+                    n += kind.page_bytes(need, self.page_size, store.element_size()) // self.page_size
         return n
 
+    def fixed_bytes_per_request(self) -> int:
+        """Bytes of fixed-size state (recurrent states, convolution tails) one live request owns."""
+        return sum(kind.fixed_bytes(need) for units in self._units for need, kind, _ in units if not kind.paged)
+
     def storage_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.storage.values())
+        return sum(store.numel() * store.element_size() for units in self._units for _n, _k, store in units)
 
     def check(self) -> None:
         """Every page is either free or in exactly one table; raises CacheError otherwise."""

@@ -72,13 +72,11 @@ def plan_cache(needs: list, *, page_size: int, parallel: int, ctx: int, batch: i
     """`needs[s]`: the state need of cache slot s (or None).  `pool_tokens`, when given, replaces `parallel * ctx` as
     the size of a group without a window (a caller that knows its requests are short).  `budget_bytes`: what the
     cache may take (None: no limit)."""
-    from .kinds import kind_of
+    from .kinds import flatten_need, kind_of
     groups: dict = {}
     order: list = []
     fixed = 0
-    for s, need in enumerate(needs):
-        if need is None:
-            continue
+    for s, need in ((s, part) for s, whole in enumerate(needs) for part in flatten_need(whole)):
         kind = kind_of(need)
         if not kind.paged:
             fixed += parallel * kind.fixed_bytes(need)
@@ -93,7 +91,8 @@ def plan_cache(needs: list, *, page_size: int, parallel: int, ctx: int, batch: i
                               _ceil_div(window + min(batch, ctx) + page_size, page_size) * page_size)
             g = groups[window] = GroupPlan(window, per_req, 0, 0)
             order.append(window)
-        g.slots.append(s)
+        if s not in g.slots:
+            g.slots.append(s)
         g.bytes_per_page += kind.page_bytes(need, page_size, element_size)
     full_tokens = pool_tokens if pool_tokens is not None else parallel * _ceil_div(ctx, page_size) * page_size
     for g in groups.values():

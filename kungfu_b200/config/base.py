@@ -98,8 +98,10 @@ def read_config_json(path: str) -> dict:
 
 
 def architecture_name(raw: dict, where: str = "config.json") -> str:
-    """The model class a config.json asks for: `architectures[0]`."""
+    """The model class a config.json asks for: `architectures[0]`, or the string under `architecture`."""
+    if "architectures" not in raw and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names (or 'architecture' a name)")
     return archs[0]

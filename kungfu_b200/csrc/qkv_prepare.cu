@@ -1,0 +1,154 @@
+// What stands between the q|k|v projection and the attention kernels, for mixers that do more there than rotate:
+// one warp per (row, head) takes a head of q, k or v through
+//   1. an optional bias and short causal convolution over time (short_conv.cuh; the state is read here and moved on
+//      afterwards by kf_short_conv_commit),
+//   2. for q and k an optional RMS norm over the head, x / sqrt(mean(x^2) + eps) * w, one weight vector shared by all heads,
+//   3. for q and k the rotation of the first `rot` elements by the step's cos/sin table, pairs (2i, 2i+1) when
+//      `interleaved`, else (i, i + rot/2),
+// and stores q as a row of the attention's query matrix and k, v at the token's place in the request's pages.
+// Keys and values may have different sizes dk and dv; queries and pages use D >= max(dk, dv) elements per head and the
+// tail is zero (a zero tail changes neither q.k nor the first dv elements of the weighted sum of values).
+// Input layout per row: [ nh*dk | nkv*dk | nkv*dv ] starting at column col0 of a 32-bit matrix with ld columns.
+// Page layout: pages[page][0 = key | 1 = value][kv head][slot in page][D].
+// Everything is computed in 32-bit; only the stores round.
+#include "short_conv.cuh"
+
+constexpr int QP_MAX_D = 256;
+constexpr int QP_WARPS = 4;
+
+template <typename TW, typename TQ, typename TKV>
+__global__ void __launch_bounds__(QP_WARPS * 32)
+qkv_prepare_kernel(KfConvIn cv, const TW* __restrict__ conv_w, const TW* __restrict__ q_norm, const TW* __restrict__ k_norm,
+                   float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int interleaved,
+                   int nh, int nkv, int dk, int dv, int D, const int* __restrict__ positions,
+                   const int* __restrict__ row_req, const int* __restrict__ req_row_start,
+                   const int* __restrict__ req_state_slot, const int* __restrict__ block_table, int table_stride,
+                   int page_size, TKV* __restrict__ pages, TQ* __restrict__ q_out, int write_kv, int T) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ float hs[QP_WARPS][QP_MAX_D];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slots = nh + 2 * nkv;
+  const long item = (long)blockIdx.x * QP_WARPS + warp;
+  if (item >= (long)T * slots) return;                      // whole warps leave; only __syncwarp below
+  const int t = (int)(item / slots), hslot = (int)(item - (long)t * slots);
+  const int req = row_req[t];
+  const int kind = hslot < nh ? 0 : (hslot < nh + nkv ? 1 : 2);            // query, key, value
+  const int head = kind == 0 ? hslot : (kind == 1 ? hslot - nh : hslot - nh - nkv);
+  if (req < 0) {                                            // padding row: a zero query, nothing filed
+    if (kind == 0)
+      for (int i = lane; i < D; i += 32) kf_store(q_out, ((size_t)t * nh + head) * D + i, 0.f);
+    return;
+  }
+  if (kind != 0 && !write_kv) return;
+  const int d = kind == 2 ? dv : dk;
+  const int chan0 = kind == 0 ? head * dk : (kind == 1 ? nh * dk + head * dk : (nh + nkv) * dk + head * dv);
+  const int row0 = req_row_start[req], slot = req_state_slot[req];
+  float* x = hs[warp];
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    float v;
+    if (conv_w) v = kf_conv_value<TW>(cv, conv_w, row0, slot, t - row0, chan0 + i);
+    else v = kf_conv_input<TW>(cv, t, 0, 0, chan0 + i);     // no convolution: the row's own (biased) value
+    x[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const TW* nw = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
+  if (nw) {
+    ss = kf_warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)d + eps);
+    for (int i = lane; i < d; i += 32) x[i] = x[i] * inv * kf_load(nw, i);
+  }
+  __syncwarp();
+  // destination of this head
+  TQ* qo = nullptr;
+  TKV* po = nullptr;
+  if (kind == 0) {
+    qo = q_out + ((size_t)t * nh + head) * D;
+  } else {
+    const int pos = positions[t];
+    const int page = block_table[(size_t)req * table_stride + pos / page_size];
+    if (page < 0) return;                                   // never for a reserved position; guards the store
+    po = pages + ((((size_t)page * 2 + (kind - 1)) * nkv + head) * page_size + (pos % page_size)) * D;
+  }
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)t * half;
+  const float* s = sin_t + (size_t)t * half;
+  for (int i = lane; i < D; i += 32) {
+    float v = 0.f;
+    if (i < d) {
+      v = x[i];
+      if (kind != 2 && i < rot) {
+        if (interleaved) {
+          const int pr = i >> 1;
+          v = (i & 1) ? fmaf(x[i], c[pr], x[i - 1] * s[pr]) : fmaf(x[i], c[pr], -x[i + 1] * s[pr]);
+        } else {
+          v = i < half ? fmaf(x[i], c[i], -x[i + half] * s[i]) : fmaf(x[i], c[i - half], x[i - half] * s[i - half]);
+        }
+      }
+    }
+    if (kind == 0) kf_store(qo, i, v);
+    else kf_store(po, i, v);
+  }
+}
+
+KF_API int kf_qkv_prepare(const float* in, int ld, int col0, const void* in_bias, const void* conv_w, int taps,
+                          const float* conv_state, const void* q_norm, const void* k_norm, int w_dtype, float eps,
+                          const float* cos_t, const float* sin_t, int rot, int interleaved, int nh, int nkv, int dk, int dv,
+                          int D, const int* positions, const int* row_req, const int* req_row_start,
+                          const int* req_state_slot, const int* block_table, int table_stride, int page_size,
+                          void* pages, int kv_dtype, void* q_out, int q_dtype, int write_kv, int T, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  if (D > QP_MAX_D || dk > D || dv > D || dk < 1 || dv < 1 || rot > dk || (rot & 1) || taps > KF_MAX_TAPS) return KF_ERR_SIZE;
+  if (rot > 0 && (!cos_t || !sin_t)) return KF_ERR_SIZE;
+  if (!conv_w) taps = 1;
+  KfConvIn cv{in, ld, col0, in_bias, conv_state, nh * dk + nkv * dk + nkv * dv, taps};
+  const long n_work = (long)T * (nh + 2 * nkv);
+  const dim3 grid((unsigned)((n_work + QP_WARPS - 1) / QP_WARPS));
+#define KF_GO(TW, TQ, TKV)                                                                                              \
+  kf_launch(qkv_prepare_kernel<TW, TQ, TKV>, grid, dim3(QP_WARPS * 32), 0, stream, cv, (const TW*)conv_w,                \
+            (const TW*)q_norm, (const TW*)k_norm, eps, cos_t, sin_t, rot, interleaved, nh, nkv, dk, dv, D, positions,     \
+            row_req, req_row_start, req_state_slot, block_table, table_stride, page_size, (TKV*)pages, (TQ*)q_out,      \
+            write_kv, T)
+  if (w_dtype == KF_F32 && q_dtype == KF_F32 && kv_dtype == KF_F32) KF_GO(float, float, float);
+  else if (w_dtype == KF_BF16 && q_dtype == KF_BF16 && kv_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// The per-head output gate and the packing of the attention's result: out[t][h*dv + i] = o[t][h*D + i] * sigmoid(g[t][h]),
+// g read from column gcol0 + h of a 32-bit matrix with ld columns (null: no gate, only the packing).
+template <typename TQ>
+__global__ void head_gate_kernel(const TQ* __restrict__ o, const float* __restrict__ g, int ld, int gcol0, int nh, int dv,
+                                 int D, TQ* __restrict__ out, const int* __restrict__ row_req) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int t = blockIdx.x;
+  const bool pad = row_req[t] < 0;
+  for (int e = threadIdx.x; e < nh * dv; e += blockDim.x) {
+    const int h = e / dv, i = e - h * dv;
+    float v = 0.f;
+    if (!pad) {
+      v = kf_load(o, ((size_t)t * nh + h) * D + i);
+      if (g) v *= 1.f / (1.f + expf(-g[(size_t)t * ld + gcol0 + h]));
+    }
+    kf_store(out, (size_t)t * nh * dv + e, v);
+  }
+}
+
+KF_API int kf_head_gate(const void* o, const float* g, int ld, int gcol0, int nh, int dv, int D, void* out, int dtype,
+                        const int* row_req, int T, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  const int threads = nh * dv >= 1024 ? 256 : 128;
+  if (dtype == KF_F32)
+    kf_launch(head_gate_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, g, ld, gcol0, nh, dv, D, (float*)out, row_req);
+  else if (dtype == KF_BF16)
+    kf_launch(head_gate_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)o, g, ld, gcol0, nh, dv, D,
+              (__nv_bfloat16*)out, row_req);
+  else
+    return KF_ERR_DTYPE;
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

@@ -372,6 +372,16 @@ def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
     _check(library().kf_gated_act(_p(gu), _dt(gu), _p(out), _dt(out), T, I, _ACT[activation], _stream()), "gated_act")
 
 
+@_dispatch("linear_act")
+def linear_act(x, w_up, out, activation: str, ctx) -> None:
+    """out[T, I] = act(x . Wup^T): the first half of a feed-forward without a gate."""
+    T = x.shape[0]
+    I = out.shape[1]
+    up = ctx.buf("ffn_up", (T, I), torch.float32)
+    linear(x, w_up, up)
+    activation_(up, out, activation)
+
+
 @_dispatch("rope_table")
 def rope_table(positions, inv_freq, cos, sin) -> None:
     """cos/sin[t, i] of positions[t] * inv_freq[i], 32-bit."""
@@ -518,6 +528,101 @@ def rope_append_attend(qkv, cos, sin, rot: int, out, ctx, cache, n_heads: int, n
                                          cache.page_size, n_heads, n_kv_heads, head_dim, _f(scale), _f(softcap),
                                          int(window or 0), splits.value, _p(partial), _p(sc["counters"]), _stream()),
            "attention (decode, rotation and append inside)")
+
+
+# ---- short convolutions, the q|k|v preparation of mixers that convolve and norm their heads, the state-space scan ----
+
+_CONV_ACT = {None: 0, "none": 0, "silu": 1}
+
+
+@_dispatch("short_conv")
+def short_conv(proj, col0: int, in_bias, weight, out_bias, act, state, out, ctx) -> None:
+    """out[t, c] = act(sum_j weight[c, j] * u_(t - taps + 1 + j)[c] + out_bias[c]) over the rows of every request of the step,
+    u = proj[:, col0 + c] + in_bias[c]; rows before the step come from `state` [requests, taps - 1, C] (32-bit), zeros
+    before the sequence's start.  `proj` and `out` are 32-bit."""
+    T = out.shape[0]
+    C, taps = weight.shape
+    _check(library().kf_short_conv(_p(proj), proj.shape[1], int(col0), _p(in_bias), _p(weight), _p(out_bias), _dt(weight), C,
+                                   taps, _CONV_ACT[act], _p(state), _p(out), out.shape[1], _p(ctx.row_req),
+                                   _p(ctx.req_row_start), _p(ctx.req_state_slot), T, _stream()), "short_conv")
+
+
+@_dispatch("short_conv_commit")
+def short_conv_commit(proj, col0: int, in_bias, n_channels: int, taps: int, state, ctx, w_dtype=None) -> None:
+    """After every reader of the old state has been launched: state[slot] <- the last taps - 1 inputs of each request."""
+    if taps <= 1:
+        return
+    dt = _dt(in_bias) if in_bias is not None else (BF16 if w_dtype == torch.bfloat16 else F32)
+    _check(library().kf_short_conv_commit(_p(proj), proj.shape[1], int(col0), _p(in_bias), dt, int(n_channels), int(taps),
+                                          _p(state), ctx.n_reqs, _p(ctx.req_row_start), _p(ctx.req_n_rows),
+                                          _p(ctx.req_state_slot), _stream()), "short_conv_commit")
+
+
+@_dispatch("qkv_prepare")
+def qkv_prepare(proj, col0: int, in_bias, conv_w, conv_state, q_norm, k_norm, eps: float, cos, sin, rot: int,
+                interleaved: bool, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, ctx, cache, q_out) -> None:
+    """From the 32-bit q|k|v projection to the attention's operands: optional bias, short convolution (reading
+    `conv_state`), per-head RMS norm of q and k, rotation (interleaved pairs or halves), q into `q_out`
+    [T, n_heads * D] and k, v into the pages of `cache`, D = the pages' head size, tails zero."""
+    T = q_out.shape[0]
+    D = cache.pages.shape[-1]
+    if q_out.shape[1] != n_heads * D:
+        raise KernelError(f"qkv_prepare: q rows of {q_out.shape[1]} elements for {n_heads} heads of {D}")
+    table = ctx.block_tables[cache.group]
+    taps = conv_w.shape[1] if conv_w is not None else 1
+    wdt = _dt(conv_w) if conv_w is not None else _dt(q_out)
+    for w in (in_bias, q_norm, k_norm):
+        if w is not None and _dt(w) != wdt:
+            raise KernelError("qkv_prepare: bias, convolution and norm weights must share one element type")
+    _check(library().kf_qkv_prepare(_p(proj), proj.shape[1], int(col0), _p(in_bias), _p(conv_w), taps, _p(conv_state),
+                                    _p(q_norm), _p(k_norm), wdt, _f(eps), _p(cos), _p(sin), int(rot), int(interleaved),
+                                    n_heads, n_kv_heads, key_dim, value_dim, D, _p(ctx.positions), _p(ctx.row_req),
+                                    _p(ctx.req_row_start), _p(ctx.req_state_slot), _p(table), table.shape[1],
+                                    cache.page_size, _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out),
+                                    int(cache.writes), T, _stream()), "qkv_prepare")
+
+
+@_dispatch("head_gate")
+def head_gate(o, proj, gate_col0: int, n_heads: int, value_dim: int, head_dim: int, out, ctx) -> None:
+    """out[t, h * value_dim + i] = o[t, h * head_dim + i] * sigmoid(proj[t, gate_col0 + h]); proj None: packing only."""
+    T = out.shape[0]
+    _check(library().kf_head_gate(_p(o), _p(proj), proj.shape[1] if proj is not None else 0, int(gate_col0), n_heads,
+                                  value_dim, head_dim, _p(out), _dt(out), _p(ctx.row_req), T, _stream()), "head_gate")
+
+
+@_dispatch("ssm_scan")
+def ssm_scan(xbc, proj, dt_col0: int, dt_bias, a_log, d_skip, state, y, heads: int, groups: int, head_dim: int,
+             state_dim: int, ctx, writes: bool = True) -> None:
+    """The state-space recurrence over the rows of every request of the step, from and into `state`
+    [requests, heads, head_dim, state_dim] (32-bit): S = exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x, with
+    dt = softplus(proj[:, dt_col0 + h] + dt_bias[h]); xbc rows are [x | B | C] (32-bit)."""
+    _check(library().kf_ssm_scan(_p(xbc), xbc.shape[1], _p(proj), proj.shape[1], int(dt_col0), _p(dt_bias), _p(a_log),
+                                 _p(d_skip), _dt(a_log), _p(state), _p(y), heads, groups, head_dim, state_dim, ctx.n_reqs,
+                                 _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes),
+                                 _stream()), "ssm_scan")
+
+
+@_dispatch("gated_group_norm")
+def gated_group_norm(y, proj, z_col0: int, weight, eps: float, parts: int, out, ctx) -> None:
+    """out = rms norm, in `parts` equal parts of the row, of y * silu(proj[:, z_col0:z_col0 + inner]), times weight."""
+    T, inner = out.shape
+    _check(library().kf_gated_group_norm(_p(y), _p(proj), proj.shape[1], int(z_col0), _p(weight), _dt(weight), _f(eps), inner,
+                                         int(parts), _p(out), _dt(out), _p(ctx.row_req), T, _stream()), "gated_group_norm")
+
+
+@_dispatch("add2_rmsnorm")
+def add2_rmsnorm(a, b, x, *, next_weight=None, next_eps: float = 0.0, next_plus_one: bool = False, next_out=None) -> None:
+    """x += a + b (b may be None), 32-bit; if next_out is given, next_out = rmsnorm(x) * g_next in the same pass."""
+    T, H = x.shape
+    _check(library().kf_add2_rmsnorm(_p(a), _p(b), _p(x), _p(next_weight), _dt(next_weight) if next_weight is not None else F32,
+                                     _f(next_eps), int(next_plus_one), _p(next_out),
+                                     _dt(next_out) if next_out is not None else F32, T, H, _stream()), "add2_rmsnorm")
+
+
+@_dispatch("activation")
+def activation_(x, out, act: str) -> None:
+    """out = act(x), x 32-bit."""
+    _check(library().kf_activation(_p(x), _p(out), _dt(out), ctypes.c_long(x.numel()), _ACT[act], _stream()), "activation")
 
 
 @_dispatch("argmax")

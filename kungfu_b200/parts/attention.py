@@ -16,7 +16,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Mixer, PagedKV, PositionEncoding, register_mixer
+from .base import FixedState, Mixer, PagedKV, PositionEncoding, StateBundle, register_mixer
+from .conv import ShortConv
 
 
 class PagedAttention(Mixer):
@@ -65,3 +66,86 @@ class PagedAttention(Mixer):
 
 
 register_mixer("paged_attention", PagedAttention)
+
+
+class ConvGatedAttention(Mixer):
+    """Grouped-query attention whose q, k and v pass more than a rotation on their way from the projection, and whose
+    heads are gated on their way out.  In order, every step optional except the attention itself:
+
+      [q | k | v | g] = x W_in^T (+ bias on q, k, v)          one product over the stacked matrix
+      q, k, v <- short causal convolution over time, per channel (`conv`, state: the last taps - 1 projected rows)
+      q, k <- RMS norm over each head, one weight vector for all heads (`q_norm`, `k_norm`)
+      q, k <- rotation of the first rotary dims by `position` (its `interleaved` flag chooses the pairing)
+      k, v written to the request's pages; o = softmax(softcap(q . k * scale)) v, causal, optionally windowed
+      o_h <- o_h * sigmoid(g_h)                                one gate per head, from the same input x
+      y = o W_o^T
+
+    Keys and values may have different head sizes (`key_dim`, `value_dim`); the cache holds heads of
+    D = max of the two (rounded up to even) with zero tails, so the framework's attention kernels serve both.
+    Scores, softmax, norms, the rotation and the gate are 32-bit."""
+
+    def __init__(self, w_in: torch.Tensor, wo: torch.Tensor, *, n_heads: int, n_kv_heads: int, key_dim: int,
+                 value_dim: int, scale: float, softcap: float = 0.0, window: int | None = None,
+                 position: PositionEncoding | None = None, bias: torch.Tensor | None = None,
+                 conv: ShortConv | None = None, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                 norm_eps: float = 1e-6, gated: bool = False):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"n_heads {n_heads} is not a multiple of n_kv_heads {n_kv_heads}")
+        self.w_in, self.wo, self.bias = w_in, wo, bias
+        self.n_heads, self.n_kv_heads = int(n_heads), int(n_kv_heads)
+        self.key_dim, self.value_dim = int(key_dim), int(value_dim)
+        self.head_dim = (max(self.key_dim, self.value_dim) + 1) // 2 * 2
+        self.scale, self.softcap = float(scale), float(softcap)
+        self.window = None if window is None else int(window)
+        self.position, self.conv = position, conv
+        self.q_norm, self.k_norm, self.norm_eps = q_norm, k_norm, float(norm_eps)
+        self.gated = bool(gated)
+        self.qkv_width = (self.n_heads + self.n_kv_heads) * self.key_dim + self.n_kv_heads * self.value_dim
+        self.proj_width = self.qkv_width + (self.n_heads if self.gated else 0)
+        self.width = wo.shape[0]
+        if w_in.numel() and w_in.shape[0] != self.proj_width:
+            raise ValueError(f"stacked projection has shape {tuple(w_in.shape)}, expected {self.proj_width} rows")
+        if conv is not None and conv.channels != self.qkv_width:
+            raise ValueError(f"the convolution has {conv.channels} channels, q|k|v have {self.qkv_width}")
+        rot = getattr(position, "rotary_dims", 0) if position is not None else 0
+        if rot > self.key_dim:
+            raise ValueError(f"{rot} rotary dims for keys of {self.key_dim}")
+        ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim)
+
+    def state_need(self):
+        kv = PagedKV(self.n_kv_heads, self.head_dim, self.window)
+        if self.conv is None or self.conv.taps <= 1:
+            return kv
+        return StateBundle((kv, self.conv.state_need()))
+
+    def forward(self, x, ctx, cache):
+        kv, tail = cache if isinstance(cache, tuple) else (cache, None)
+        T = x.shape[0]
+        nh, nkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        proj = ctx.buf("attn_proj", (T, self.proj_width), torch.float32)
+        ops.linear(x, self.w_in, proj)
+        if self.position is not None:
+            cos, sin = self.position.rotation(ctx)
+            rot, interleaved = 2 * cos.shape[1], bool(getattr(self.position, "interleaved", False))
+        else:
+            cos = sin = None
+            rot, interleaved = 0, False
+        q = ctx.buf("attn_q", (T, nh * D), ctx.act_dtype)
+        conv = self.conv
+        ops.qkv_prepare(proj, 0, self.bias, conv.weight if conv else None, tail.state if tail is not None else None,
+                        self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, nh, nkv, self.key_dim,
+                        self.value_dim, ctx, kv, q)
+        if tail is not None:
+            conv.commit(proj, 0, self.bias, ctx, tail)
+        o = ctx.buf("attn_o", (T, nh * D), ctx.act_dtype)
+        ops.paged_attention(q, o, ctx, kv, nh, nkv, D, self.scale, self.softcap, self.window)
+        if self.gated or D != self.value_dim:
+            packed = ctx.buf("attn_gated", (T, nh * self.value_dim), ctx.act_dtype)
+            ops.head_gate(o, proj if self.gated else None, self.qkv_width, nh, self.value_dim, D, packed, ctx)
+            o = packed
+        y = ctx.buf("branch_out", (T, self.width), torch.float32)
+        ops.linear(o, self.wo, y)
+        return y
+
+
+register_mixer("conv_gated_attention", ConvGatedAttention)

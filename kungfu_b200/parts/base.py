@@ -38,7 +38,14 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
-StateNeed = PagedKV | FixedState
+@dataclass(frozen=True)
+class StateBundle:
+    """Several states behind one cache slot (keys and values in pages plus the last inputs of a short convolution; a
+    recurrent state plus the same): the mixer's forward gets a tuple of views, one per part, in this order."""
+    parts: tuple
+
+
+StateNeed = PagedKV | FixedState | StateBundle
 
 
 # ---- part kinds -----------------------------------------------------------------------------------

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, register_block
+from .norm import RmsNorm
 
 
 class SandwichBlock(Block):
@@ -44,3 +45,28 @@ class SandwichBlock(Block):
 
 
 register_block("sandwich", SandwichBlock)
+
+
+class ParallelBlock(Block):
+    """Mixer and feed-forward side by side on ONE normed input: h = norm(x); x <- x + (mixer(h) + ffn(h)).
+    `ffn` may be None (a layer without a feed-forward).  The two branch results and the residual are summed in one
+    32-bit kernel that also computes the next block's norm when that is an RMS norm."""
+    fuses_next_norm = True
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: FeedForward | None):
+        self.pre_mixer, self.mixer, self.ffn = norm, mixer, ffn
+
+    def forward(self, x, ctx, cache, normed=None, then=None):
+        act = ctx.act_dtype
+        h = normed if normed is not None else self.pre_mixer.forward(x, ctx, act)
+        a = self.mixer.forward(h, ctx, cache)
+        f = self.ffn.forward(h, ctx) if self.ffn is not None else None
+        if isinstance(then, RmsNorm):
+            nxt = ctx.buf("norm_out", (x.shape[0], then.width), act)       # h is dead once both branches have run
+            ops.add2_rmsnorm(a, f, x, next_weight=then.weight, next_eps=then.eps, next_plus_one=then.plus_one, next_out=nxt)
+            return x, nxt
+        ops.add2_rmsnorm(a, f, x)
+        return x, (then.forward(x, ctx, act) if then is not None else None)
+
+
+register_block("parallel", ParallelBlock)

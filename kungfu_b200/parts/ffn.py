@@ -38,3 +38,28 @@ class GatedFfn(FeedForward):
 
 
 register_feed_forward("gated", GatedFfn)
+
+
+class DenseFfn(FeedForward):
+    """The feed-forward without a gate: y = act(x Wup^T) Wdown^T."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, activation: str = "gelu_tanh"):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {ACTIVATIONS}")
+        if w_up.shape[0] != w_down.shape[1]:
+            raise ValueError("the up matrix must have as many rows as the down matrix has columns")
+        self.w_up, self.w_down = w_up, w_down
+        self.activation = activation
+        self.inner = w_down.shape[1]
+        self.width = w_down.shape[0]
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        h = ctx.buf("ffn_h", (T, self.inner), ctx.act_dtype)
+        ops.linear_act(x, self.w_up, h, self.activation, ctx)
+        y = ctx.buf("ffn_out", (T, self.width), torch.float32)
+        ops.linear(h, self.w_down, y)
+        return y
+
+
+register_feed_forward("dense", DenseFfn)

@@ -8,8 +8,16 @@ reference: crates/kf-backend-cpu/src/rope.rs:18-37,57-108 and gemma2.rs:19):
 The inverse frequencies are computed once in 64-bit and rounded to 32-bit; the angle,
 its cosine and sine are 32-bit and are tabulated once per step for all layers that
 share this part.
+
+Two options for other models.  `interleaved`: the pair is (x_{2i}, x_{2i+1}) instead; the table is the same, and
+the mixer's kernel reads `interleaved` to know which elements a table column turns.  `scaling`
+(factor, low, high, original): the frequency rescaling for long contexts in the manner of Llama 3.1, by wavelength
+l = 2 pi / f: f is kept where l < original / high, divided by factor where l > original / low, and blended
+linearly in between with s = (original / l - low) / (high - low): (1 - s) f / factor + s f.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -18,7 +26,8 @@ from .base import PositionEncoding, register_position
 
 
 class Rope(PositionEncoding):
-    def __init__(self, head_dim: int, base: float, device, rotary_dims: int | None = None):
+    def __init__(self, head_dim: int, base: float, device, rotary_dims: int | None = None, *,
+                 interleaved: bool = False, scaling: dict | None = None):
         self.head_dim = int(head_dim)
         self.rotary_dims = int(rotary_dims if rotary_dims is not None else head_dim)
         if self.rotary_dims % 2 or self.rotary_dims > self.head_dim:
@@ -27,6 +36,17 @@ class Rope(PositionEncoding):
         half = self.rotary_dims // 2
         idx = torch.arange(half, dtype=torch.float64)
         inv = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * idx / self.rotary_dims)
+        self.interleaved = bool(interleaved)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            factor, low, high = (float(self.scaling[k]) for k in ("factor", "low", "high"))
+            original = float(self.scaling["original"])
+            if not (factor > 0 and high > low and original > 0):
+                raise ValueError(f"rotary scaling needs factor > 0, high > low and original > 0, found {self.scaling}")
+            wavelength = 2.0 * math.pi / inv
+            blend = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+            mixed = (1.0 - blend) * inv / factor + blend * inv
+            inv = torch.where(wavelength < original / high, inv, torch.where(wavelength > original / low, inv / factor, mixed))
         self.inv_freq = inv.to(torch.float32).to(device)
 
     def rotation(self, ctx):

@@ -52,6 +52,9 @@ def _register_builtin() -> None:
     from .config.gemma2 import Gemma2Config
     from .models import gemma2
     register("Gemma2ForCausalLM", Gemma2Config.from_dict, gemma2.build, gemma2.tensor_specs, replace=True)
+    from .config.bolonex import BolonexConfig
+    from .models import bolonex
+    register("Bolonex", BolonexConfig.from_dict, bolonex.build, bolonex.tensor_specs, replace=True)
 
 
 _register_builtin()

@@ -114,6 +114,138 @@ class CpuOps:
                 p = torch.softmax(s, dim=0)
                 out[t, h * d:(h + 1) * d] = (p @ V[:, h // group]).to(out.dtype)
 
+    # ---- short convolution, q|k|v preparation, state-space scan (mirrors of the kernels' contracts) ----------------
+    @staticmethod
+    def _conv_inputs(proj, col0, in_bias, C, taps, state, ctx, req):
+        """[taps - 1 + n, C]: the state of request `req` followed by its biased inputs of this step."""
+        r0, n, slot = int(ctx.req_row_start[req]), int(ctx.req_n_rows[req]), int(ctx.req_state_slot[req])
+        u = proj[r0:r0 + n, col0:col0 + C].float()
+        if in_bias is not None:
+            u = u + in_bias.float()[None, :]
+        old = state[slot, :taps - 1].float() if (state is not None and taps > 1) else torch.zeros(0, C)
+        return torch.cat([old, u], 0), r0, n, slot
+
+    def short_conv(self, proj, col0, in_bias, weight, out_bias, act, state, out, ctx):
+        C, taps = weight.shape
+        for req in range(ctx.n_reqs):
+            if int(ctx.req_n_rows[req]) <= 0:
+                continue
+            u, r0, n, _ = self._conv_inputs(proj, col0, in_bias, C, taps, state, ctx, req)
+            y = torch.zeros(n, C)
+            for j in range(taps):
+                y += u[j:j + n] * weight[:, j].float()[None, :]
+            if out_bias is not None:
+                y = y + out_bias.float()[None, :]
+            if act == "silu":
+                y = y * torch.sigmoid(y)
+            out[r0:r0 + n] = y
+
+    def short_conv_commit(self, proj, col0, in_bias, n_channels, taps, state, ctx, w_dtype=None):
+        if taps <= 1:
+            return
+        for req in range(ctx.n_reqs):
+            if int(ctx.req_n_rows[req]) <= 0:
+                continue
+            u, _, _, slot = self._conv_inputs(proj, col0, in_bias, n_channels, taps, state, ctx, req)
+            state[slot, :taps - 1] = u[-(taps - 1):]
+
+    def qkv_prepare(self, proj, col0, in_bias, conv_w, conv_state, q_norm, k_norm, eps, cos, sin, rot, interleaved,
+                    nh, nkv, dk, dv, ctx, cache, q_out):
+        T = q_out.shape[0]
+        D = cache.pages.shape[-1]
+        C = (nh + nkv) * dk + nkv * dv
+        x = torch.zeros(T, C)
+        if conv_w is not None:
+            self.short_conv(proj, col0, in_bias, conv_w, None, None, conv_state, x, ctx)
+        else:
+            x = proj[:, col0:col0 + C].float() + (in_bias.float()[None, :] if in_bias is not None else 0.0)
+        q = x[:, :nh * dk].reshape(T, nh, dk).clone()
+        k = x[:, nh * dk:(nh + nkv) * dk].reshape(T, nkv, dk).clone()
+        v = x[:, (nh + nkv) * dk:].reshape(T, nkv, dv)
+        for y, w in ((q, q_norm), (k, k_norm)):
+            if w is not None:
+                y.copy_(y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w.float())
+        if rot:
+            c, s_ = cos[:, None, :], sin[:, None, :]
+            for y in (q, k):
+                if interleaved:
+                    a, b = y[..., 0:rot:2].clone(), y[..., 1:rot:2].clone()
+                    y[..., 0:rot:2] = a * c - b * s_
+                    y[..., 1:rot:2] = b * c + a * s_
+                else:
+                    a, b = y[..., :rot // 2].clone(), y[..., rot // 2:rot].clone()
+                    y[..., :rot // 2] = a * c - b * s_
+                    y[..., rot // 2:rot] = a * s_ + b * c
+        qp = torch.zeros(T, nh, D)
+        qp[..., :dk] = q
+        valid = (ctx.row_req[:T] >= 0)
+        qp[~valid] = 0
+        q_out.copy_(qp.reshape(T, nh * D).to(q_out.dtype))
+        if not cache.writes:
+            return
+        table = ctx.block_tables[cache.group]
+        P = cache.page_size
+        for t in range(T):
+            r = int(ctx.row_req[t])
+            if r < 0:
+                continue
+            pos = int(ctx.positions[t])
+            page = int(table[r, pos // P])
+            assert page >= 0
+            cache.pages[page, :, :, pos % P, :] = 0
+            cache.pages[page, 0, :, pos % P, :dk] = k[t].to(cache.pages.dtype)
+            cache.pages[page, 1, :, pos % P, :dv] = v[t].to(cache.pages.dtype)
+
+    def head_gate(self, o, proj, gate_col0, nh, dv, D, out, ctx):
+        T = out.shape[0]
+        y = o.float().view(T, nh, D)[..., :dv]
+        if proj is not None:
+            y = y * torch.sigmoid(proj[:, gate_col0:gate_col0 + nh].float())[..., None]
+        y = y * (ctx.row_req[:T] >= 0).float()[:, None, None]
+        out.copy_(y.reshape(T, nh * dv).to(out.dtype))
+
+    def ssm_scan(self, xbc, proj, dt_col0, dt_bias, a_log, d_skip, state, y, heads, groups, P, N, ctx, writes=True):
+        inner = heads * P
+        A = -torch.exp(a_log.float())
+        for req in range(ctx.n_reqs):
+            n = int(ctx.req_n_rows[req])
+            if n <= 0:
+                continue
+            r0, slot = int(ctx.req_row_start[req]), int(ctx.req_state_slot[req])
+            S = state[slot].clone()                                   # [heads, P, N]
+            for i in range(n):
+                row = xbc[r0 + i]
+                dt = torch.nn.functional.softplus(proj[r0 + i, dt_col0:dt_col0 + heads].float() + dt_bias.float(), threshold=20.0)
+                for h in range(heads):
+                    g = h // (heads // groups)
+                    x = row[h * P:(h + 1) * P]
+                    B = row[inner + g * N:inner + (g + 1) * N]
+                    C = row[inner + groups * N + g * N:inner + groups * N + (g + 1) * N]
+                    S[h] = torch.exp(A[h] * dt[h]) * S[h] + dt[h] * torch.outer(x, B)
+                    y[r0 + i, h * P:(h + 1) * P] = S[h] @ C + d_skip[h].float() * x
+            if writes:
+                state[slot] = S
+
+    def gated_group_norm(self, y, proj, z_col0, weight, eps, parts, out, ctx):
+        T, inner = out.shape
+        z = proj[:, z_col0:z_col0 + inner].float()
+        v = (y * (z * torch.sigmoid(z))).view(T, parts, inner // parts)
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        v = v.reshape(T, inner) * weight.float()[None, :]
+        v = torch.where((ctx.row_req[:T] >= 0)[:, None], v, torch.zeros_like(v))
+        out.copy_(v.to(out.dtype))
+
+    def add2_rmsnorm(self, a, b, x, *, next_weight=None, next_eps=0.0, next_plus_one=False, next_out=None):
+        x.add_(a if b is None else a + b)
+        if next_out is not None:
+            self.rmsnorm(x, next_weight, next_eps, next_plus_one, next_out)
+
+    def activation(self, x, out, act):
+        out.copy_(_act(act, x.float()).to(out.dtype))
+
+    def linear_act(self, x, w_up, out, activation, ctx):
+        out.copy_(_act(activation, x.float() @ w_up.float().T).to(out.dtype))
+
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(torch.int32))
 
