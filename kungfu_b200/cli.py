@@ -76,17 +76,25 @@ def cmd_inspect(args) -> int:
         total_bytes += info.nbytes
         total_params += info.numel
         parts = n.split(".")
-        gid = f"layer.{parts[2]}" if n.startswith("model.layers.") else ("embedding" if "embed" in n else "output")
+        if n.startswith("model.layers."):
+            gid = f"layer.{parts[2]}"
+        elif len(parts[0]) > 1 and parts[0][0] == "l" and parts[0][1:].isdigit():
+            gid = f"layer.{parts[0][1:]}"
+        else:
+            gid = "embedding" if "embed" in n else "output"
         g = groups.setdefault(gid, {"id": gid, "bytes": 0, "elements": 0, "count": 0})
         g["bytes"] += info.nbytes
         g["elements"] += info.numel
         g["count"] += 1
     elt = 2
-    states = [{"layer": l, "kind": "kv_cache", "bytes_per_token": 2 * cfg.num_key_value_heads * cfg.head_dim * elt,
-               "window": cfg.window_of(l), "fixed_bytes": 0} for l in range(cfg.num_hidden_layers)]
+    if hasattr(cfg, "state_summary"):                      # an architecture whose layers keep more than keys and values
+        states = cfg.state_summary(elt)
+    else:
+        states = [{"layer": l, "kind": "kv_cache", "bytes_per_token": 2 * cfg.num_key_value_heads * cfg.head_dim * elt,
+                   "window": cfg.window_of(l), "fixed_bytes": 0} for l in range(cfg.num_hidden_layers)]
     doc = {"architecture": cfg.architecture, "tensors": len(tensors), "bytes": total_bytes, "params": total_params,
            "dtypes": hist, "hparams": cfg.to_dict(), "layers": cfg.num_hidden_layers,
-           "context_train": cfg.max_position_embeddings, "groups": list(groups.values()), "states": states,
+           "context_train": getattr(cfg, "max_position_embeddings", None), "groups": list(groups.values()), "states": states,
            "missing": missing, "unexpected": unexpected, "wrong_shape": wrong}
     if args.json:
         print(json.dumps(doc))
@@ -96,12 +104,15 @@ def cmd_inspect(args) -> int:
         print(f"dtypes        {hist}")
         print(f"layers        {doc['layers']}  context_train {doc['context_train']}")
         for k, v in doc["hparams"].items():
-            if k != "layer_types":
+            if k not in ("layer_types", "layers"):
                 print(f"  {k:32s} {v}")
+        for i, l in enumerate(doc["hparams"].get("layers", [])):
+            print(f"  layer {i:3d} {l['type']:10s} mixer {l['mixer']} mlp {l['mlp']}" + (f" weights_of {l['weights_of']}" if "weights_of" in l else ""))
         for g in doc["groups"]:
             print(f"group {g['id']:12s} tensors {g['count']:3d}  bytes {g['bytes']}")
         for s in states:
-            print(f"state layer {s['layer']:3d} kv_cache bytes_per_token {s['bytes_per_token']} window {s['window']}")
+            print(f"state layer {s['layer']:3d} {s['kind']} bytes_per_token {s['bytes_per_token']} window {s['window']} "
+                  f"fixed_bytes {s['fixed_bytes']}")
     if missing or unexpected or wrong:
         print(f"error: weights do not match the configuration: missing {missing}, unexpected {unexpected}, "
               f"wrong shapes {wrong}", file=sys.stderr)
@@ -286,7 +297,7 @@ def cmd_random_weights(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="kungfu", description="Gemma 2 on B200: inspect, describe, generate, score, bench")
+    ap = argparse.ArgumentParser(prog="kungfu", description="Gemma 2 and Bolonex on B200: inspect, describe, generate, score, bench")
     sub = ap.add_subparsers(dest="cmd", required=True)
     p = sub.add_parser("inspect", help="what the folder is, how its tensors group, what state each layer keeps")
     p.add_argument("model")

@@ -168,7 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     auto finish = [&](float v, float u) -> float {
       if (EPI == EPI_GATED) return act_fast(v, act) * u;
       if (EPI == EPI_F32) return kf_softcap(v, softcap);
-      return v;
+      return act > 0 ? act_fast(v, act - 1) : v;                               // bfloat16 store: act - 1 names an activation
     };
     auto store = [&](int t, float r) {
       if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
@@ -442,7 +442,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             float r;
             if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
             else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
-            else r = v[j];
+            else r = act > 0 ? act_fast(v[j], act - 1) : v[j];
             if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
             else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
           }
@@ -744,7 +744,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
               float r;
               if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
               else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
-              else r = v[j];
+              else r = act > 0 ? act_fast(v[j], act - 1) : v[j];
               if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
               else ((__nv_bfloat16*)out)[(size_t)t * ld_out + f] = __float2bfloat16_rn(r);
             }
@@ -802,7 +802,7 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
 template <int EPI>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_split_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                          void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int stages, int splits,
+                          void* __restrict__ out, int T, int N, int K, int ld_out, float softcap, int act, int stages, int splits,
                           int* __restrict__ error_flag) {
   constexpr int PN = 256;
   constexpr int A_BYTES = BM * BK * 2, BH_BYTES = (PN / 2) * BK * 2;
@@ -962,6 +962,10 @@ gemm_tc_pair_split_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
           else
             for (int j = 0; j < 4; ++j) if (f + j < N) o[j] = r[j];
         } else {
+          if (act > 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[j] = act_fast(r[j], act - 1);
+          }
           __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)t * ld_out + f;
           if (vec) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
@@ -1381,13 +1385,13 @@ int pair_split_capacity(int splits) {
 
 template <int EPI>
 int launch_pair_split(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int ld_out, float softcap,
-                      int splits, int* error_flag, cudaStream_t stream) {
+                      int act, int splits, int* error_flag, cudaStream_t stream) {
   if (!pair_split_configure<EPI>()) return KF_ERR_SETUP;
   const int n_tiles = kf_ceil_div(N, 2 * BM) * kf_ceil_div(T, 256);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   pair_split_config<EPI>(&cfg, attr, n_tiles, splits, stream);
-  cudaLaunchKernelEx(&cfg, gemm_tc_pair_split_kernel<EPI>, tw, tx, out, T, N, K, ld_out, softcap, PAIR_SPLIT_STAGES, splits, error_flag);
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_split_kernel<EPI>, tw, tx, out, T, N, K, ld_out, softcap, act, PAIR_SPLIT_STAGES, splits, error_flag);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }
@@ -1493,7 +1497,8 @@ KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_ou
   return plan_linear(T, N_features, K, gated, bn_out, splits_out);
 }
 
-// mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out, 2 = gated: w = [gate; up] stacked
+// mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out (act > 0: activation act - 1 on the way out, the
+// first half of a feed-forward without a gate), 2 = gated: w = [gate; up] stacked
 // ([2*N, K]), out[T, N] = act(gate) * up in bfloat16.  `partial` must hold splits * T * (gated ? 2N : N) floats when
 // the plan says splits > 1; `counters` one zero-initialised int per output tile (they are left zero).
 KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, float softcap, int act,
@@ -1514,8 +1519,8 @@ KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T
     const int nkb = (K + BK - 1) / BK, kb_per = (nkb + splits - 1) / splits;
     const int sp = (nkb + kb_per - 1) / kb_per;                    // no empty split
     if (sp == splits) {
-      if (mode == EPI_F32) return launch_pair_split<EPI_F32>(tw, txp, out, T, N, K, N, softcap, splits, error_flag, stream);
-      return launch_pair_split<EPI_BF16>(tw, txp, out, T, N, K, N, softcap, splits, error_flag, stream);
+      if (mode == EPI_F32) return launch_pair_split<EPI_F32>(tw, txp, out, T, N, K, N, softcap, 0, splits, error_flag, stream);
+      return launch_pair_split<EPI_BF16>(tw, txp, out, T, N, K, N, softcap, act, splits, error_flag, stream);
     }
   }
   if (g_pair && splits == 1 && bn == 256) {

@@ -57,8 +57,11 @@ class Engine:
                 self.cfg, model = api.random_model(config, seed, dtype=dtype, device=self.device)
             else:
                 raise ValueError("Engine needs a model folder or a configuration")
-            trained = getattr(self.cfg, "max_position_embeddings", 8192)
-            n_ctx = trained if ctx == "auto" else min(int(ctx), trained) if ctx else trained
+            trained = getattr(self.cfg, "max_position_embeddings", None)      # None: the architecture names no trained length
+            if trained is None:
+                n_ctx = 8192 if (ctx == "auto" or not ctx) else int(ctx)
+            else:
+                n_ctx = trained if ctx == "auto" else min(int(ctx), trained) if ctx else trained
             page = page_size or api.DEFAULT_PAGE_SIZE
             if events:
                 _events.enabled = True

@@ -377,6 +377,9 @@ def linear_act(x, w_up, out, activation: str, ctx) -> None:
     """out[T, I] = act(x . Wup^T): the first half of a feed-forward without a gate."""
     T = x.shape[0]
     I = out.shape[1]
+    # bfloat16: the activation is the product's own epilogue (the code act + 1 on its bfloat16 store)
+    if out.dtype == torch.bfloat16 and _linear_tc(x, w_up, out, 1, I, 0.0, _ACT[activation] + 1):
+        return
     up = ctx.buf("ffn_up", (T, I), torch.float32)
     linear(x, w_up, up)
     activation_(up, out, activation)

@@ -114,7 +114,7 @@ class CpuOps:
                 p = torch.softmax(s, dim=0)
                 out[t, h * d:(h + 1) * d] = (p @ V[:, h // group]).to(out.dtype)
 
-    # ---- short convolution, q|k|v preparation, state-space scan (mirrors of the kernels' contracts) ----------------
+    # ---- short convolution, q|k|v preparation, state-space scan (restatements of what the kernels of the same names do) ----------------
     @staticmethod
     def _conv_inputs(proj, col0, in_bias, C, taps, state, ctx, req):
         """[taps - 1 + n, C]: the state of request `req` followed by its biased inputs of this step."""

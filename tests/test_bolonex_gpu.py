@@ -1,0 +1,517 @@
+"""Bolonex on the GPU against the plain implementation (tests/plain_bolonex.py, float64, whole sequences).
+
+First every mechanism alone, kernel by kernel, on a hand-made step of several requests (some with earlier tokens in
+their state, one padding row); then the model through the step function in every way of cutting the work, in 32-bit
+on sharp weights and in bfloat16; then long decoding, far keys, used-again slots, generation through the engine,
+and the programs in bin/.
+"""
+import json
+import os
+import subprocess
+import sys
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import bolonex_cases as bx
+import helpers
+import plain_bolonex as pb
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 2e-4, "bfloat16": 4e-2}
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+# ---- a hand-made step: three requests with 5, 1 and 3 rows, the second and third with tokens before the step ------------
+
+class FakeStep:
+    """The integers a step's kernels read, for requests of `rows` rows that already hold `before` tokens, in state slots
+    `slots`; one padding row (request -1) at the end and one request slot without rows."""
+
+    def __init__(self, rows=(5, 1, 3), before=(0, 7, 2), slots=(2, 0, 3)):
+        self.rows, self.before, self.slots = rows, before, slots
+        row_req, pos, start = [], [], []
+        for r, (n, b) in enumerate(zip(rows, before)):
+            start.append(len(row_req))
+            row_req += [r] * n
+            pos += list(range(b, b + n))
+        row_req.append(-1)
+        pos.append(0)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        self.n_rows, self.n_reqs = len(row_req), len(rows) + 1
+        self.row_req, self.positions = i32(row_req), i32(pos)
+        self.req_row_start, self.req_n_rows = i32(start + [0]), i32(list(rows) + [0])
+        self.req_state_slot = i32(list(slots) + [0])
+        self.act_dtype = torch.float32
+
+    def buf(self, tag, shape, dtype):
+        return torch.empty(shape, dtype=dtype, device=DEV)
+
+    def real_rows(self, r):
+        a = int(self.req_row_start[r])
+        return slice(a, a + self.rows[r])
+
+
+def _rel(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max()) / max(float(b.double().abs().max()), 1e-30)
+
+
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps,act,bias", [(4, "silu", True), (2, None, False), (1, None, True), (8, "silu", False)])
+def test_short_convolution_with_state_and_its_commit(wdtype, taps, act, bias):
+    from kungfu_b200 import ops
+    st = FakeStep()
+    g = torch.Generator().manual_seed(taps)
+    C, ld, col0 = 37, 50, 6
+    w = (0.5 * torch.randn(C, taps, generator=g)).to(DTYPES[wdtype])
+    in_b = (0.3 * torch.randn(C, generator=g)).to(DTYPES[wdtype]) if bias else None
+    out_b = (0.3 * torch.randn(C, generator=g)).to(DTYPES[wdtype]) if bias else None
+    # whole histories of the three requests; the step holds the last rows, the state what stood before them
+    hist = [torch.randn(b + n, ld, generator=g) for n, b in zip(st.rows, st.before)]
+    proj = torch.zeros(st.n_rows, ld)
+    state = torch.full((4, max(taps - 1, 1), C), 9.0)               # slot 1 is nobody's and must stay as it is
+    for r, h in enumerate(hist):
+        proj[st.real_rows(r)] = h[st.before[r]:]
+        u = h[:, col0:col0 + C] + (in_b.float() if bias else 0.0)
+        tail = torch.cat([torch.zeros(taps, C), u[:st.before[r]]])[-(taps - 1):] if taps > 1 else torch.zeros(1, C)
+        state[st.slots[r]] = tail
+    proj_d, state_d = proj.to(DEV), state.to(DEV)
+    out = torch.full((st.n_rows, C), 5.0, device=DEV)
+    ops.short_conv(proj_d, col0, None if in_b is None else in_b.to(DEV), w.to(DEV), None if out_b is None else out_b.to(DEV),
+                   act, state_d, out, st)
+    ops.short_conv_commit(proj_d, col0, None if in_b is None else in_b.to(DEV), C, taps, state_d, st, w_dtype=w.dtype)
+    for r, h in enumerate(hist):
+        u = (h[:, col0:col0 + C] + (in_b.float() if bias else 0.0)).double()
+        y = pb.short_conv(u, w, out_b)
+        if act == "silu":
+            y = pb.silu(y)
+        assert _rel(out[st.real_rows(r)], y[st.before[r]:]) < 1e-5
+        if taps > 1:
+            want = torch.cat([torch.zeros(taps, C, dtype=torch.float64), u])[-(taps - 1):]
+            assert _rel(state_d[st.slots[r]], want) < 1e-6
+    assert float(state_d[1].min()) == 9.0 and float(out[-1].min()) == 5.0      # untouched: no request, padding row
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,dk,dv,rot,interleaved,taps", [(4, 2, 16, 24, 8, True, 3), (3, 3, 32, 16, 32, True, 4),
+                                                                (5, 1, 20, 20, 20, False, 1), (2, 1, 64, 64, 0, True, 2)])
+def test_q_k_v_preparation_then_attention(dtype, nh, nkv, dk, dv, rot, interleaved, taps):
+    """bias -> convolution -> head norm -> rotation -> pages, then the framework's attention over those pages and the
+    head gate, against the plain attention mixer run on each request's whole history (projection and output matrix
+    are left out: they are the identity here)."""
+    from kungfu_b200 import ops
+    from kungfu_b200.cache.kinds import PagedKVView
+    st = FakeStep(rows=(5, 1, 3), before=(0, 9, 4))
+    tdt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(nh * 100 + dk)
+    C = (nh + nkv) * dk + nkv * dv
+    ld = C + nh
+    D = (max(dk, dv) + 1) // 2 * 2
+    page = 4
+    m = {"heads": nh, "kv_heads": nkv, "dim": dk, "vdim": dv, "scale": 0.3, "softcap": 7.0,
+         "rot": {"base": 50.0, "dims": rot} if rot else None}
+    t = {"l.mix.q.norm": (2.0 + 0.3 * torch.randn(dk, generator=g)).to(tdt), "l.mix.k.norm": (2.0 + 0.3 * torch.randn(dk, generator=g)).to(tdt)}
+    bias = (0.2 * torch.randn(C, generator=g)).to(tdt)
+    conv = (0.6 * torch.randn(C, taps, generator=g)).to(tdt)
+    hist = [torch.randn(b + n, ld, generator=g) for n, b in zip(st.rows, st.before)]
+    # the plain mixer takes h and matrices; with identity matrices h IS the projection: split it by hand instead
+    def plain(h):
+        T = h.shape[0]
+        u = h[:, :C].double() + bias.double()
+        y = pb.short_conv(u, conv)
+        q = pb.rms(y[:, :nh * dk].view(T, nh, dk), 1e-5) * t["l.mix.q.norm"].double()
+        k = pb.rms(y[:, nh * dk:(nh + nkv) * dk].view(T, nkv, dk), 1e-5) * t["l.mix.k.norm"].double()
+        v = y[:, (nh + nkv) * dk:].view(T, nkv, dv)
+        if rot:
+            if interleaved:
+                q, k = pb.rotate_interleaved(q, m["rot"]), pb.rotate_interleaved(k, m["rot"])
+            else:
+                f = pb.rotary_frequencies(m["rot"])
+                ang = torch.arange(T, dtype=torch.float64)[:, None] * f[None, :]
+                c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                def turn(x):
+                    a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+                    return torch.cat([a * c - b * s, a * s + b * c, x[..., rot:]], -1)
+                q, k = turn(q), turn(k)
+        gate = torch.sigmoid(h[:, C:].double())
+        seen = torch.tril(torch.ones(T, T, dtype=torch.bool))
+        out = torch.empty(T, nh, dv, dtype=torch.float64)
+        for head in range(nh):
+            s = (q[:, head] @ k[:, head // (nh // nkv)].T) * 0.3
+            s = 7.0 * torch.tanh(s / 7.0)
+            out[:, head] = (torch.softmax(s.masked_fill(~seen, float("-inf")), -1) @ v[:, head // (nh // nkv)]) * gate[:, head:head + 1]
+        return out.reshape(T, nh * dv)
+
+    # device state: pages and block tables as the manager would hand them out, filled by running the history in two steps
+    n_pages = 16
+    pages = torch.zeros(n_pages, 2, nkv, page, D, dtype=tdt, device=DEV)
+    view = PagedKVView(pages, page, 0, True)
+    tab = torch.full((3, 8), -1, dtype=torch.int32)                    # by request, whatever step it appears in
+    nxt = 3                                                             # pages in a scattered order
+    for r, (n, b) in enumerate(zip(st.rows, st.before)):
+        for i in range(-(-(n + b) // page)):
+            tab[r, i] = (nxt * 5) % n_pages
+            nxt += 1
+    conv_state = torch.zeros(4, max(taps - 1, 1), C, device=DEV)
+    inv = torch.tensor([50.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32, device=DEV) if rot else None
+
+    def run(step, who, rows_of):
+        table = torch.full((step.n_reqs, 8), -1, dtype=torch.int32)
+        table[:len(who)] = tab[who]
+        step.block_tables = [table.to(DEV)]
+        step.n_dec_rows = step.n_pre_rows = step.n_tiles = step.n_wide = 0
+        step.max_kv_len = 16
+        proj = torch.zeros(step.n_rows, ld)
+        for r, rows in rows_of.items():
+            proj[step.real_rows(r)] = rows
+        proj = proj.to(DEV)
+        cos = sin = None
+        if rot:
+            cos = torch.empty(step.n_rows, rot // 2, device=DEV)
+            sin = torch.empty_like(cos)
+            ops.rope_table(step.positions, inv, cos, sin)
+        q = torch.empty(step.n_rows, nh * D, dtype=tdt, device=DEV)
+        ops.qkv_prepare(proj, 0, bias.to(DEV), conv.to(DEV), conv_state, t["l.mix.q.norm"].to(DEV), t["l.mix.k.norm"].to(DEV),
+                        1e-5, cos, sin, rot, interleaved, nh, nkv, dk, dv, step, view, q)
+        ops.short_conv_commit(proj, 0, bias.to(DEV), C, taps, conv_state, step, w_dtype=conv.dtype)
+        o = torch.empty_like(q)
+        ops.paged_attention(q, o, step, view, nh, nkv, D, 0.3, 7.0, None)
+        packed = torch.empty(step.n_rows, nh * dv, dtype=tdt, device=DEV)
+        ops.head_gate(o, proj, C, nh, dv, D, packed, step)
+        return packed
+
+    first = FakeStep(rows=(9, 4), before=(0, 0), slots=(st.slots[1], st.slots[2]))      # what requests 1 and 2 held before
+    run(first, [1, 2], {0: hist[1][:9], 1: hist[2][:4]})
+    got = run(st, [0, 1, 2], {r: hist[r][st.before[r]:] for r in range(3)})
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    for r in range(3):
+        assert _rel(got[st.real_rows(r)], plain(hist[r])[st.before[r]:]) < tol
+    assert float(got[-1].abs().max()) == 0.0                              # the padding row
+
+
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,groups,P,N", [(2, 1, 16, 16), (6, 3, 8, 40), (3, 3, 12, 10), (4, 2, 64, 128), (2, 2, 40, 256)])
+def test_state_space_scan_in_portions(wdtype, heads, groups, P, N):
+    """The recurrence over a step of several requests, some of which start from a state that an earlier step left."""
+    from kungfu_b200 import ops
+    st = FakeStep(rows=(11, 1, 3), before=(0, 20, 9))
+    g = torch.Generator().manual_seed(heads * 7 + N)
+    inner = heads * P
+    ld_x, ld_p, dt0 = inner + 2 * groups * N, heads + 5, 3
+    a_log = (-3.0 + 2.5 * torch.rand(heads, generator=g)).to(DTYPES[wdtype])
+    dt_bias = (0.5 * torch.randn(heads, generator=g)).to(DTYPES[wdtype])
+    d_skip = torch.randn(heads, generator=g).to(DTYPES[wdtype])
+    hist_x = [torch.randn(b + n, ld_x, generator=g) for n, b in zip(st.rows, st.before)]
+    hist_p = [2.0 * torch.randn(b + n, ld_p, generator=g) for n, b in zip(st.rows, st.before)]
+    hist_p[0][3, dt0] = 30.0                                            # softplus far out on both sides
+    hist_p[0][4, dt0] = -30.0
+
+    def plain(x, p):
+        T = x.shape[0]
+        dt = pb.softplus(p[:, dt0:dt0 + heads].double() + dt_bias.double())
+        A = -torch.exp(a_log.double())
+        y = torch.empty(T, heads, P, dtype=torch.float64)
+        S_all = []
+        for h in range(heads):
+            gi = h // (heads // groups)
+            S = torch.zeros(N, P, dtype=torch.float64)
+            for i in range(T):
+                xs = x[i, h * P:(h + 1) * P].double()
+                B = x[i, inner + gi * N:inner + (gi + 1) * N].double()
+                C = x[i, inner + groups * N + gi * N:inner + groups * N + (gi + 1) * N].double()
+                S = torch.exp(A[h] * dt[i, h]) * S + dt[i, h] * torch.outer(B, xs)
+                y[i, h] = S.T @ C + d_skip[h].double() * xs
+            S_all.append(S)
+        return y.reshape(T, inner), torch.stack(S_all)
+
+    state = torch.full((4, heads, P, N), 3.0, device=DEV)
+    state[list(st.slots)] = 0.0
+
+    def run(step, xs, ps):
+        xbc, proj = torch.zeros(step.n_rows, ld_x), torch.zeros(step.n_rows, ld_p)
+        for r in xs:
+            xbc[step.real_rows(r)], proj[step.real_rows(r)] = xs[r], ps[r]
+        y = torch.full((step.n_rows, inner), 5.0, device=DEV)
+        ops.ssm_scan(xbc.to(DEV), proj.to(DEV), dt0, dt_bias.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, y, heads, groups,
+                     P, N, step)
+        return y
+
+    first = FakeStep(rows=(20, 9), before=(0, 0), slots=(st.slots[1], st.slots[2]))
+    run(first, {0: hist_x[1][:20], 1: hist_x[2][:9]}, {0: hist_p[1][:20], 1: hist_p[2][:9]})
+    y = run(st, {r: hist_x[r][st.before[r]:] for r in range(3)}, {r: hist_p[r][st.before[r]:] for r in range(3)})
+    for r in range(3):
+        ref_y, ref_S = plain(hist_x[r], hist_p[r])
+        assert _rel(y[st.real_rows(r)], ref_y[st.before[r]:]) < 2e-5
+        assert _rel(state[st.slots[r]], ref_S.transpose(1, 2)) < 2e-5          # stored [head][p][n]
+    assert float(state[1].min()) == 3.0 and float(y[-1].min()) == 5.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inner,parts", [(32, 1), (48, 2), (36, 3), (512, 2), (4096, 4)])
+def test_gated_group_norm(dtype, inner, parts):
+    from kungfu_b200 import ops
+    st = FakeStep()
+    g = torch.Generator().manual_seed(inner)
+    y = 3.0 * torch.randn(st.n_rows, inner, generator=g)
+    proj = 2.0 * torch.randn(st.n_rows, inner + 9, generator=g)
+    w = (1.0 + 0.3 * torch.randn(inner, generator=g)).to(DTYPES[dtype])
+    out = torch.empty(st.n_rows, inner, dtype=DTYPES[dtype], device=DEV)
+    ops.gated_group_norm(y.to(DEV), proj.to(DEV), 4, w.to(DEV), 1e-5, parts, out, st)
+    v = y.double() * pb.silu(proj[:, 4:4 + inner].double())
+    ref = pb.rms(v.view(-1, parts, inner // parts), 1e-5).reshape(-1, inner) * w.double()
+    assert _rel(out[:-1], ref[:-1]) < (1e-5 if dtype == "float32" else 1e-2)
+    assert float(out[-1].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,two", [(64, True), (100, False), (2304, True)])
+def test_residual_of_two_branches_and_the_next_norm(dtype, H, two):
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(H)
+    a, b, x = (torch.randn(7, H, generator=g) for _ in range(3))
+    w = (0.1 * torch.randn(H, generator=g)).to(DTYPES[dtype])
+    xd = x.to(DEV)
+    nxt = torch.empty(7, H, dtype=DTYPES[dtype], device=DEV)
+    ops.add2_rmsnorm(a.to(DEV), b.to(DEV) if two else None, xd, next_weight=w.to(DEV), next_eps=1e-5, next_plus_one=True, next_out=nxt)
+    ref = x.double() + a.double() + (b.double() if two else 0.0)
+    assert _rel(xd, ref) < 1e-6
+    assert _rel(nxt, pb.norm_one_plus(ref, w, 1e-5)) < (1e-5 if dtype == "float32" else 1e-2)
+    x2 = x.to(DEV)
+    ops.add2_rmsnorm(a.to(DEV), b.to(DEV) if two else None, x2)
+    assert _rel(x2, ref) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,K,I", [(5, 64, 96), (70, 512, 1024), (300, 512, 1024), (600, 1024, 512), (3, 100, 70)])
+def test_feed_forward_without_a_gate(dtype, T, K, I):
+    """The up product with the activation as its epilogue (bfloat16, every launch shape of the product) or as a
+    kernel of its own (32-bit, rows that are no multiple of 16 bytes)."""
+    from kungfu_b200 import ops
+    st = FakeStep()
+    g = torch.Generator().manual_seed(T + K)
+    x = torch.randn(T, K, generator=g).to(DTYPES[dtype])
+    w = (torch.randn(I, K, generator=g) / K ** 0.5 * 2.0).to(DTYPES[dtype])
+    out = torch.empty(T, I, dtype=DTYPES[dtype], device=DEV)
+    ops.linear_act(x.to(DEV), w.to(DEV), out, "gelu_tanh", st)
+    ref = pb.gelu_tanh(x.double() @ w.double().T)
+    assert _rel(out, ref) < (1e-5 if dtype == "float32" else 1e-2)
+    ops.raise_on_device_error(torch.device(DEV))
+
+
+# ---- the model through the step function -------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    cases = dict(bx.CASES)
+    cases["E"] = (bx.BX_E, [3, 130, 64, 200, 65, 17], 64)
+    for name, (cfg, lengths, page) in cases.items():
+        for sharp in (False, True):
+            folder = bx.write_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=21, sharp=sharp)
+            reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab"], 300 + i) for i, n in enumerate(lengths)}
+            tensors = helpers.read_tensors(folder)
+            ref = {rid: pb.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+            out[(name, sharp)] = (folder, cfg, reqs, ref, page)
+    return out
+
+
+def _runner(folder, dtype, page, max_tokens, max_requests=4, graphs=True, ctx=2048):
+    from kungfu_b200 import api
+    cfg, model = api.load_model(folder, dtype=dtype, device=DEV)
+    return api.make_runner(cfg, model, dtype=dtype, device=DEV, page_size=page, max_tokens=max_tokens,
+                           max_requests=max_requests, max_context=ctx, cuda_graphs=graphs)
+
+
+def _check(got, ref, tol):
+    """32-bit: the largest difference of any logit against the largest logit, below `tol` at every place.
+    bfloat16 (tol >= 1e-2): per place, the root mean square of the differences against that of the place's logits.
+    Rounding to 8 bits at every product input is amplified unevenly by these small random models (a head whose
+    convolved values nearly cancel is divided by a tiny root mean square; the plain implementation with the same
+    roundings shows the same few places 5 to 30 % off), so the bound is on the distribution: half of the places
+    within tol / 2, nineteen in twenty within 2 tol, none beyond 0.5.  A wrong key, page or state moves most places by
+    order 1; the 32-bit runs on sharp weights are the strict comparison."""
+    assert got
+    if tol < 1e-2:
+        scale = max(float(r.abs().max()) for r in ref.values())
+        worst = max(float((row - ref[rid][pos]).abs().max()) for (rid, pos), row in got.items()) / scale
+        assert worst < tol, f"rel err {worst:.3e}"
+        return
+    errs = sorted(float((row - ref[rid][pos]).pow(2).mean().sqrt() / ref[rid][pos].pow(2).mean().sqrt())
+                  for (rid, pos), row in got.items())
+    mid, high, top = errs[len(errs) // 2], errs[min(len(errs) - 1, (len(errs) * 19) // 20)], errs[-1]
+    assert mid < tol / 2 and high < 2 * tol and top < 0.5, f"rel err median {mid:.3e}, 95 % {high:.3e}, max {top:.3e}"
+
+
+def _steps(mode, reqs):
+    return {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 32),
+            "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=5)}[mode](reqs)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+@pytest.mark.parametrize("dtype,sharp", [("float32", True), ("bfloat16", False)])
+def test_modes_match_plain(models, name, mode, dtype, sharp):
+    """Whole prompts, most of a prompt then token by token, portions of 2 to 11 tokens, and mixed batches of up to four
+    unequal requests with pools so small that pages and state slots are used again."""
+    from kungfu_b200 import ops
+    folder, cfg, reqs, ref, page = models[(name, sharp)]
+    steps = _steps(mode, reqs)
+    runner = _runner(folder, dtype, page, helpers.trace_max_tokens(steps, page))
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _check(got, ref, TOL[dtype])
+    ops.raise_on_device_error(torch.device(DEV))
+    assert runner.cache.n_live == 0
+    if mode == "mixed":
+        assert all(n > g.pool.n_pages for n, g in zip(runner.cache.pages_handed_out(), runner.cache.groups))
+
+
+@pytest.mark.parametrize("name,page", [("A", 4), ("E", 64)])
+def test_batch_of_unequal_requests_equals_each_alone(models, name, page):
+    """32-bit: the logits of a request must not depend on what else is in its step (beyond rounding of sums)."""
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, reqs, ref, _ = models[(name, True)]
+    runner = _runner(folder, "float32", page, 1024, graphs=False)
+    alone = {}
+    for rid, toks in reqs.items():
+        runner.cache.add_request(rid)
+        alone[rid] = runner.step([StepEntry(rid, toks, [len(toks) - 1])])[0].clone()
+        runner.cache.release(rid)
+    some = list(reqs)[:4]
+    for rid in some:
+        runner.cache.add_request(rid)
+    together = runner.step([StepEntry(rid, reqs[rid], [len(reqs[rid]) - 1]) for rid in some]).clone()
+    for i, rid in enumerate(some):
+        scale = float(ref[rid].abs().max())
+        assert float((together[i] - alone[rid]).abs().max()) / scale < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_long_decoding_from_captured_graphs(models, name, dtype):
+    """A short prompt and then 150 tokens one by one (the decode steps replay from a CUDA graph after the second)."""
+    folder, cfg, _, _, page = models[(name, dtype == "float32")]
+    toks = helpers.random_tokens(160, cfg["vocab"], 9)
+    ref = {"a": pb.forward(cfg, helpers.read_tensors(folder), toks).float()}
+    steps = helpers.trace_decode_tail({"a": toks}, 150)
+    runner = _runner(folder, dtype, page, 192)
+    got = helpers.run_trace_with_runner(runner, steps)
+    _check(got, ref, TOL[dtype])
+    assert any(s.get("graph") is not None for s in runner._graphs.values())
+
+
+def test_far_keys_and_old_state_carry_the_result(models):
+    """Keys hundreds of tokens back, across page borders, in a prompt and in decoding; and the books of this test: with
+    the sharp draw, losing one far page of keys or one request's recurrent state moves the logits by far more than the
+    tolerance, so a fault there would show."""
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, _, _, page = models[("E", True)]
+    toks = helpers.random_tokens(600, cfg["vocab"], 77)
+    ref = pb.forward(cfg, helpers.read_tensors(folder), toks).float()
+    scale = float(ref.abs().max())
+    runner = _runner(folder, "float32", page, 1024, graphs=False)
+    runner.cache.add_request("a")
+    want = [0, 1, 2, 3, 62, 63, 64, 65, 127, 128, 129, 300, 447, 448, 449, 575]
+    got = runner.step([StepEntry("a", toks[:576], want)]).cpu()
+    for k, p in enumerate(want):
+        assert float((got[k] - ref[p]).abs().max()) / scale < TOL["float32"], p
+    for p in range(576, 590):
+        row = runner.step([StepEntry("a", [toks[p]], [0])])[0].cpu()
+        assert float((row - ref[p]).abs().max()) / scale < TOL["float32"], p
+    # the books: knock out the first page of the first attention layer, then the recurrent state, and look at the next token
+    kv = runner.cache.storage[0][0]
+    table = runner.cache.block_table(0, "a")
+    saved = kv[table[0]].clone()
+    kv[table[0]].zero_()
+    row = runner.step([StepEntry("a", [toks[590]], [0])])[0].cpu()
+    assert float((row - ref[590]).abs().max()) / scale > 20 * TOL["float32"]
+    kv[table[0]] = saved
+    memory = runner.cache.storage[1][0]
+    memory[runner.cache.state_slot("a")].zero_()
+    row = runner.step([StepEntry("a", [toks[591]], [0])])[0].cpu()
+    assert float((row - ref[591]).abs().max()) / scale > 20 * TOL["float32"]
+
+
+def test_a_state_slot_that_is_used_again_starts_from_zero(models):
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, reqs, ref, page = models[("B", True)]
+    runner = _runner(folder, "float32", page, 128, max_requests=1, graphs=False)
+    for rid in ("r3", "r2", "r3"):
+        toks = reqs[rid]
+        runner.cache.add_request(rid)
+        assert runner.cache.state_slot(rid) == 0
+        a = runner.step([StepEntry(rid, toks[:2], [1])]).cpu()
+        b = runner.step([StepEntry(rid, toks[2:], [len(toks) - 3])]).cpu()
+        runner.cache.release(rid)
+        scale = float(ref[rid].abs().max())
+        assert float((a[0] - ref[rid][1]).abs().max()) / scale < TOL["float32"]
+        assert float((b[0] - ref[rid][len(toks) - 1]).abs().max()) / scale < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generate_through_the_entry_point(models, dtype):
+    """Greedy generation through Engine (scheduler, portions under a token budget, tokens drawn on the device, graphs)
+    against the plain implementation's best token at every place, near ties aside."""
+    import kungfu_b200
+    from kungfu_b200.sampling import Sampling
+    folder, cfg, reqs, _, page = models[("E", False)]
+    tensors = helpers.read_tensors(folder)
+    eng = kungfu_b200.Engine(folder, dtype=dtype, device=DEV, ctx=512, batch=64, parallel=4, page_size=page,
+                             max_tokens_in_cache=1024)
+    prompts = [reqs["r1"], reqs["r0"], reqs["r3"], reqs["r5"], reqs["r2"]]
+    outs = eng.generate(prompts, Sampling(temperature=0.0), max_tokens=12, ignore_eos=True)
+    margin = 1e-3 if dtype == "float32" else 5e-2
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        seq = list(p)
+        for tok in o:
+            logits = pb.forward(cfg, tensors, seq)[-1]
+            top = torch.topk(logits, 2).values
+            if float(top[0] - top[1]) > margin * float(logits.abs().max()):
+                assert int(torch.argmax(logits)) == tok
+            seq.append(tok)
+
+
+def test_programs_in_bin(models, tmp_path):
+    """bin/trace_run replays a trace of a Bolonex folder; bin/kungfu inspects the folder and completes a prompt."""
+    folder, cfg, reqs, ref, page = models[("A", True)]
+    steps = helpers.trace_mixed(reqs, seed=2)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", str(helpers.trace_max_tokens(steps, 64))],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    at = {rid: 0 for rid in reqs}
+    scale = max(float(r.abs().max()) for r in ref.values())
+    for s in steps:
+        rows = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        k = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                assert float(np.abs(rows[k] - ref[e["id"]][at[e["id"]] + w].numpy()).max()) / scale < TOL["float32"]
+                k += 1
+            at[e["id"]] += len(e["tokens"])
+    kungfu = os.path.join(ROOT, "bin", "kungfu")
+    p = subprocess.run([sys.executable, kungfu, "inspect", folder, "--json"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    doc = json.loads(p.stdout)
+    assert doc["architecture"] == "Bolonex" and doc["layers"] == 4 and not doc["missing"] and not doc["unexpected"]
+    assert [s["kind"] for s in doc["states"]] == ["recurrent+conv_tail", "kv_cache+conv_tail"] * 2
+    p = subprocess.run([sys.executable, kungfu, "generate", "--model", folder, "--ids", json.dumps(reqs["r1"]), "--max-tokens", "5",
+                        "--dtype", "float32", "--ignore-eos", "--ctx", "256"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    gen = json.loads(p.stdout.strip().splitlines()[-1])["generated"]
+    tensors = helpers.read_tensors(folder)
+    seq = list(reqs["r1"])
+    for tok in gen:
+        logits = pb.forward(cfg, tensors, seq)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) > 1e-3 * float(logits.abs().max()):
+            assert int(torch.argmax(logits)) == tok
+        seq.append(tok)
