@@ -5,6 +5,9 @@
                     [--size 2b|9b|27b] [--layers L] [--batch B] [--context C] [--only-headline]
     python bench.py --micro attention|prompt-attention|gemm|products|reference
                     (kernels alone, JSON lines; for the summaries in profiles/)
+    python bench.py --compare bolonex
+                    (Bolonex beside Gemma 2 at equal layer sizes: prefill and decode throughput and, per operation, the
+                    time of one step against the time its bytes take at the measured copy rate; one JSON line)
 
 A "step" is one decode step: every live request gets one token.  Default: the layer sizes of Gemma 2 2B, random
 bfloat16 weights, 8 requests at a context of 8192 tokens.  `value` is decoded tokens per second timed with CUDA events
@@ -150,8 +153,9 @@ def fill_cache(runner, rid, n_tokens: int) -> None:
 def randomize_pages(runner, torch) -> None:
     g = torch.Generator(device=runner.device)
     g.manual_seed(1)
-    for s, t in runner.cache.storage.items():
-        if not isinstance(t, list) and t.dim() == 5:
+    stores = [t for v in runner.cache.storage.values() for t in (v if isinstance(v, list) else [v])]
+    for t in stores:
+        if t.dim() == 5:
             flat = t.view(-1)
             step = 1 << 28
             for i in range(0, flat.numel(), step):
@@ -450,6 +454,151 @@ def run_ours(args) -> dict:
             "points": {f"decode_{k}": v for k, v in points.items()},
             "decode": {k: {kk: vv for kk, vv in v.items() if kk != "clocks"} for k, v in head["decode"].items()},
             "mixed": mixed, "fp32": fp32, "sizes": sizes, "slow_kernel_fallbacks": ops.fallbacks(), "impl": "ours"}
+
+# ---- Bolonex beside Gemma 2 at equal layer sizes (--compare bolonex) ---------------------------------------------------
+# Layer sizes that resemble real models: eight layers, one attention layer to three state-space layers, the same width,
+# heads, head size, feed-forward width and vocabulary in both models (the Gemma 2 feed-forward is gated, so it has three
+# matrices of that width where Bolonex has two).
+BOLONEX_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, ssm_heads=64, ssm_vdim=64, state=128, groups=1, norm_groups=1),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, ssm_heads=128, ssm_vdim=64, state=128, groups=8, norm_groups=8),
+}
+COMPARE_VOCAB, COMPARE_LAYERS = 32000, 8
+
+
+def bolonex_config(z: dict) -> dict:
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4,
+           "scale": z["dim"] ** -0.5, "softcap": 30.0,
+           "rot": {"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    ssm = {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["state"], "groups": z["groups"],
+           "norm_groups": z["norm_groups"], "conv": 4}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "attention" if i % 4 == 0 else "mamba2", "mixer": att if i % 4 == 0 else ssm, "mlp": mlp}
+              for i in range(COMPARE_LAYERS)]
+    return {"architecture": "Bolonex", "width": z["width"], "vocab": COMPARE_VOCAB, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def gemma_twin_config(z: dict) -> dict:
+    return dict(COMMON, vocab_size=COMPARE_VOCAB, num_hidden_layers=COMPARE_LAYERS, hidden_size=z["width"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                intermediate_size=z["ff"], query_pre_attn_scalar=z["dim"], sliding_window=1 << 20,
+                layer_types=["full_attention"] * COMPARE_LAYERS)
+
+
+def bolonex_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
+    """Bytes each operation of one Bolonex step must move (bfloat16 activations, 32-bit projections and states), summed
+    over the layers that run it; for the products, the weights once plus their rows."""
+    W, H, G, d, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"]
+    sh, sp, N, sg = z["ssm_heads"], z["ssm_vdim"], z["state"], z["groups"]
+    inner, cw = sh * sp, sh * sp + 2 * sg * N
+    n_att = sum(1 for i in range(COMPARE_LAYERS) if i % 4 == 0)
+    n_ssm = COMPARE_LAYERS - n_att
+    cq = (H + 2 * G) * d
+    return {
+        "qkv_prepare": n_att * T * (4 * cq + 2 * cq + 4 * d),
+        "head_gate": n_att * T * H * d * 4,
+        "short_conv": n_ssm * T * cw * 8,
+        "short_conv_commit": n_att * n_reqs * 3 * cq * 8 + n_ssm * n_reqs * 3 * cw * 8,
+        "ssm_scan": n_ssm * (T * (cw + inner) * 4 + 2 * n_reqs * inner * N * 4),
+        "gated_group_norm": n_ssm * T * inner * 10,
+        "add2_rmsnorm": COMPARE_LAYERS * T * W * 18,
+        "paged_attention": n_att * (n_reqs * keys * 2 * G * d * 2 + T * H * d * 4),
+    }
+
+
+def gemma_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
+    W, H, G, d = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    cq = (H + 2 * G) * d
+    L = COMPARE_LAYERS
+    return {
+        "rope_kv_append": L * T * (4 * cq + 2 * cq + 4 * d),
+        "add_rmsnorm": 2 * L * T * W * 14,
+        "paged_attention": L * (n_reqs * keys * 2 * G * d * 2 + T * H * d * 4),
+        "rope_append_attend": L * (n_reqs * keys * 2 * G * d * 2 + T * (4 * cq + H * d * 2)),
+    }
+
+
+def compare_bolonex(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens tokens) and decode (--batch requests at --context tokens) of Bolonex and of
+    Gemma 2 at equal sizes, and per operation the time of one eager step beside the time its bytes would take at the
+    measured copy rate (`x_roofline`: 1.0 = at the roofline)."""
+    import torch
+    from kungfu_b200 import api, ops
+    from kungfu_b200.engine import StepEntry
+    pk, pk_src = peaks()
+    device = api.require_cuda("cuda:0")
+    ops.library()
+    T, B, ctx_len = args.prefill_tokens, args.batch, min(args.context, 4096)
+    out = {"impl": "ours", "compare": "bolonex", "peaks": pk_src, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+           "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+           "sizes": {}}
+    for name, z in BOLONEX_SIZES.items():
+        row = {}
+        for arch, raw, op_bytes in (("bolonex", bolonex_config(z), bolonex_op_bytes), ("gemma2", gemma_twin_config(z), gemma_op_bytes)):
+            cfg, model = api.random_model(raw, seed=0, dtype="bfloat16", device=device)
+            steps, warmup, reps = min(args.steps, 32), max(args.warmup, 3), args.reps
+            runner = api.make_runner(cfg, model, dtype="bfloat16", device=device, page_size=api.DEFAULT_PAGE_SIZE,
+                                     max_requests=B + 2, max_context=ctx_len + reps * steps + warmup + 192,
+                                     max_tokens=(B + 1) * (ctx_len + reps * steps + warmup + 192))
+            randomize_pages(runner, torch)
+            vocab = cfg.vocab_size
+            toks = [(i * 7919 + 13) % vocab for i in range(T)]
+            pf = []
+            for rep in range(reps + 1):
+                runner.cache.add_request("pf")
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                runner.step([StepEntry("pf", toks, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                pf.append(e0.elapsed_time(e1))
+                runner.cache.release("pf")
+            rids = [f"d{k}" for k in range(B)]
+            for r in rids:
+                fill_cache(runner, r, ctx_len - warmup)
+            ms_runs, launches = time_decode(torch, runner, rids, steps, warmup, vocab, reps)
+            # one eager prompt step and one eager decode step with every operation timed
+            traces = {}
+            runner.cache.add_request("tr")
+            ops.trace_begin()
+            runner.step([StepEntry("tr", toks, [T - 1])])
+            traces["prefill"] = (ops.trace_end(), op_bytes(z, T, 1, T))
+            runner.cache.release("tr")
+            ops.trace_begin()
+            runner.step([StepEntry(r, [(5 + k) % vocab], [0]) for k, r in enumerate(rids)])
+            traces["decode"] = (ops.trace_end(), op_bytes(z, B, B, ctx_len))
+            for r in rids:
+                runner.cache.release(r)
+            per_op = {}
+            for phase, (rec, nbytes) in traces.items():
+                agg = {}
+                for op, ms in rec:
+                    n, t = agg.get(op, (0, 0.0))
+                    agg[op] = (n + 1, t + ms)
+                total = sum(t for _, t in agg.values())
+                per_op[phase] = {"total_ms": round(total, 3), "ops": {}}
+                for op, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
+                    e = {"n": n, "us": round(t * 1e3, 1), "share": round(t / total, 3)}
+                    if op in nbytes and nbytes[op] > 0:
+                        ideal_us = nbytes[op] / (pk["hbm_gbs"] * 1e3)
+                        e["bytes"] = int(nbytes[op])
+                        e["x_roofline"] = round(t * 1e3 / ideal_us, 2)
+                    per_op[phase]["ops"][op] = e
+            m, sd = mean_sd(pf[1:])
+            d, dsd = mean_sd(ms_runs)
+            row[arch] = {"prefill": {"tokens_per_s": round(T / m * 1e3, 1), "ms": round(m, 3), "sd_ms": round(sd, 3)},
+                         "decode": {"tokens_per_s": round(B / d * 1e3, 1), "ms_per_step": round(d, 4), "sd_ms": round(dsd, 4),
+                                    "launches": int(launches)},
+                         "weight_bytes": int(model.weight_bytes()), "per_op": per_op}
+            del model, runner
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][name] = dict(row, shape=z)
+    out["slow_kernel_fallbacks"] = ops.fallbacks()
+    ops.raise_on_device_error()
+    return out
 
 
 def micro_attention() -> int:
@@ -865,7 +1014,14 @@ def main() -> int:
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
     ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
                     help="time kernels alone instead of the model step")
+    ap.add_argument("--compare", choices=["bolonex"],
+                    help="another workload: Bolonex beside Gemma 2 at equal layer sizes (prefill, decode, per-operation rooflines)")
     args = ap.parse_args()
+    if args.compare:
+        args.warmup = max(args.warmup, 3)
+        args.reps = max(args.reps, 1)
+        print(json.dumps(compare_bolonex(args)))
+        return 0
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
                 "products": lambda: micro_products(args.size), "qkv-rope": lambda: micro_qkv_rope(args.size),

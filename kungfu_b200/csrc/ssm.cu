@@ -10,30 +10,47 @@
 // The tokens of a request are walked in order, whatever the step holds of it (one token, a portion, a whole prompt),
 // so the result at a token does not depend on how the sequence was cut.
 //
-// Work split: a block owns (request, head, 32 values of p); thread (p, ns) keeps S[n][p] for n = ns, ns + 8, ... in
-// registers, eight neighbouring lanes share a p and add their partial sums of S^T C by shuffles.  Rows are staged
-// eight at a time in shared memory (dt*B, C, x, the decay), so the walk itself issues no global loads.
+// Work split: a block of 256 threads owns (request, head, 32 values of p).  Thread (pl, ns) keeps S[n][p] for two values
+// of p and every n whose group of four, n / 4, is ns modulo 16: up to 32 numbers in registers; the sixteen lanes that
+// share a pair of p add their partial sums of S^T C by shuffles.  (With eight lanes per pair and twice the registers a
+// block had four warps, one per scheduler, and issued one instruction in four cycles: every wait on shared memory or on
+// the multiply-add before it stood exposed.)  Rows are staged in shared memory, B, C, x and dt as
+// they stand in global memory, by 4-byte cp.async into a ring of two stages, so that the next rows arrive while the
+// current ones are walked; the walk itself reads 16-byte vectors (sixteen neighbouring lanes read 256 contiguous bytes)
+// and issues three packed instructions (fma.rn.f32x2: two neighbouring states each) per pair of states and no global load.  Shared rows are padded with zeros to a
+// multiple of 64 states: padded states stay zero and add nothing, so the walk has no bounds checks.
 // State layout: state[slot][head][p][n], n fastest.
 #include "common.cuh"
 
 constexpr int SSM_PC = 32;        // values of p per block
-constexpr int SSM_NS = 8;         // lanes that share a p
-constexpr int SSM_ROWS = 8;       // rows staged per round
+constexpr int SSM_NS = 16;        // lanes that share a pair of p
+constexpr int SSM_THREADS = (SSM_PC / 2) * SSM_NS;
 constexpr int SSM_MAX_N = 256;
 
-template <int NPER, typename TW>
-__global__ void __launch_bounds__(SSM_PC * SSM_NS)
+__device__ __forceinline__ void ssm_cp4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ssm_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+template <int N> __device__ __forceinline__ void ssm_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// K4: groups of four states per thread (the padded state size is 64 * K4); ROWS: rows per stage.
+template <int K4, int ROWS, typename TW>
+__global__ void __launch_bounds__(SSM_THREADS, 2)
 ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ proj, int ld_p, int dt_col0,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, float* __restrict__ y, int heads, int groups, int P, int N,
                 int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
-                const int* __restrict__ req_state_slot, int write_state) {
+                const int* __restrict__ req_state_slot, int write_state, int vec) {
+  constexpr int NP = 4 * SSM_NS * K4;                         // padded state size
+  constexpr int ROW_F = 2 * NP + SSM_PC + 4;                  // floats of one staged row: B | C | x | dt, decay, -, -
   kf_pdl_trigger();
   kf_pdl_wait();
-  __shared__ float s_dtb[SSM_ROWS][SSM_MAX_N];
-  __shared__ float s_c[SSM_ROWS][SSM_MAX_N];
-  __shared__ float s_x[SSM_ROWS][SSM_PC];
-  __shared__ float s_da[SSM_ROWS], s_dt[SSM_ROWS];
+  __shared__ __align__(16) float stage[2][ROWS][ROW_F];
   const int req = blockIdx.x / heads, h = blockIdx.x - req * heads;
   if (req >= n_reqs) return;
   const int n_rows = req_n_rows[req];
@@ -41,63 +58,119 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   const int row0 = req_row_start[req], slot = req_state_slot[req];
   const int g = h / (heads / groups);
   const int inner = heads * P;
-  const int tid = threadIdx.x, ns = tid & (SSM_NS - 1), pl = tid >> 3;
-  const int p = blockIdx.y * SSM_PC + pl;
-  const bool live = p < P;
-  float* sp = state + (((size_t)slot * heads + h) * P + (live ? p : 0)) * N;
-  float S[NPER];
-#pragma unroll
-  for (int k = 0; k < NPER; ++k) {
-    const int n = ns + SSM_NS * k;
-    S[k] = (live && n < N) ? sp[n] : 0.f;
-  }
-  const float a = -expf(kf_load(a_log, h)), bias = kf_load(dt_bias, h), dsk = kf_load(d_skip, h);
+  const int tid = threadIdx.x, ns = tid & (SSM_NS - 1), pl = tid / SSM_NS;
+  const int pbase = blockIdx.y * SSM_PC;
+  const int p0 = pbase + 2 * pl;
 
-  for (int i0 = 0; i0 < n_rows; i0 += SSM_ROWS) {
-    const int nr = min(SSM_ROWS, n_rows - i0);
-    __syncthreads();                                         // the round before has been read
-    if (tid < nr) {
-      const float z = proj[(size_t)(row0 + i0 + tid) * ld_p + dt_col0 + h] + bias;
-      const float dt = z > 20.f ? z + log1pf(expf(-z)) : log1pf(expf(z));
-      s_dt[tid] = dt;
-      s_da[tid] = expf(a * dt);
-    }
-    __syncthreads();
-    for (int idx = tid; idx < nr * N; idx += SSM_PC * SSM_NS) {
-      const int r = idx / N, n = idx - r * N;
-      const float* row = xbc + (size_t)(row0 + i0 + r) * ld_x + inner + g * N + n;
-      s_dtb[r][n] = s_dt[r] * row[0];
-      s_c[r][n] = row[(size_t)groups * N];
-    }
-    for (int idx = tid; idx < nr * SSM_PC; idx += SSM_PC * SSM_NS) {
-      const int r = idx / SSM_PC, q = idx - r * SSM_PC;
-      const int pp = blockIdx.y * SSM_PC + q;
-      s_x[r][q] = pp < P ? xbc[(size_t)(row0 + i0 + r) * ld_x + h * P + pp] : 0.f;
-    }
-    __syncthreads();
-    for (int r = 0; r < nr; ++r) {
-      const float da = s_da[r], xp = s_x[r][pl];
-      float acc = 0.f;
-#pragma unroll
-      for (int k = 0; k < NPER; ++k) {
-        const int n = ns + SSM_NS * k;
-        if (n < N) {
-          S[k] = fmaf(S[k], da, s_dtb[r][n] * xp);
-          acc = fmaf(S[k], s_c[r][n], acc);
-        }
-      }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (live && ns == 0) y[(size_t)(row0 + i0 + r) * inner + h * P + p] = fmaf(dsk, xp, acc);
-    }
+  // the zero padding: states N..NP-1 of B and C, and x beyond P (copies never write there)
+  const int pad_n = NP - N, px = min(SSM_PC, P - pbase), pad_x = SSM_PC - px;
+  for (int i = tid; i < 2 * ROWS * (2 * pad_n + pad_x); i += SSM_THREADS) {
+    const int r = i / (2 * pad_n + pad_x), j = i - r * (2 * pad_n + pad_x);
+    float* dst = (&stage[0][0][0]) + (size_t)r * ROW_F;
+    if (j < pad_n) dst[N + j] = 0.f;
+    else if (j < 2 * pad_n) dst[NP + N + j - pad_n] = 0.f;
+    else dst[2 * NP + px + j - 2 * pad_n] = 0.f;
   }
-  if (write_state && live) {
+  float2 S0[2 * K4], S1[2 * K4];                               // pairs of neighbouring states, for p0 and p0 + 1
+  float* sp0 = state + (((size_t)slot * heads + h) * P + p0) * N;
 #pragma unroll
-    for (int k = 0; k < NPER; ++k) {
-      const int n = ns + SSM_NS * k;
-      if (n < N) sp[n] = S[k];
+  for (int k = 0; k < K4; ++k)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = 4 * (ns + SSM_NS * k) + j;
+      const float v0 = (p0 < P && n < N) ? sp0[n] : 0.f, v1 = (p0 + 1 < P && n < N) ? sp0[N + n] : 0.f;
+      if (j & 1) { S0[2 * k + (j >> 1)].y = v0; S1[2 * k + (j >> 1)].y = v1; }
+      else { S0[2 * k + (j >> 1)].x = v0; S1[2 * k + (j >> 1)].x = v1; }
     }
+  const float a = -expf(kf_load(a_log, h)), bias = kf_load(dt_bias, h), dsk = kf_load(d_skip, h);
+  __syncthreads();
+
+  const int nq = N >> 2, xq = px >> 2, items = 2 * nq + xq + 1;
+  auto load = [&](int s, int i0) {                            // rows i0.. of the request into stage s
+    const int nr = min(ROWS, n_rows - i0);
+    if (vec) {                                                // 16 bytes at a time: sizes and offsets are multiples of four floats
+      for (int idx = tid; idx < nr * items; idx += SSM_THREADS) {
+        const int r = idx / items, it = idx - r * items;
+        const float* row = xbc + (size_t)(row0 + i0 + r) * ld_x;
+        float* dst = stage[s][r];
+        if (it < nq) ssm_cp16(dst + 4 * it, row + inner + g * N + 4 * it);
+        else if (it < 2 * nq) ssm_cp16(dst + NP + 4 * (it - nq), row + inner + (groups + g) * N + 4 * (it - nq));
+        else if (it < 2 * nq + xq) ssm_cp16(dst + 2 * NP + 4 * (it - 2 * nq), row + h * P + pbase + 4 * (it - 2 * nq));
+        else ssm_cp4(dst + 2 * NP + SSM_PC, proj + (size_t)(row0 + i0 + r) * ld_p + dt_col0 + h);
+      }
+    } else {
+      for (int r = 0; r < nr; ++r) {
+        const float* row = xbc + (size_t)(row0 + i0 + r) * ld_x;
+        float* dst = stage[s][r];
+        for (int n = tid; n < N; n += SSM_THREADS) {
+          ssm_cp4(dst + n, row + inner + g * N + n);
+          ssm_cp4(dst + NP + n, row + inner + (groups + g) * N + n);
+        }
+        if (tid < SSM_PC && pbase + tid < P) ssm_cp4(dst + 2 * NP + tid, row + h * P + pbase + tid);
+        if (tid == SSM_PC) ssm_cp4(dst + 2 * NP + SSM_PC, proj + (size_t)(row0 + i0 + r) * ld_p + dt_col0 + h);
+      }
+    }
+    ssm_cp_commit();
+  };
+
+  load(0, 0);
+  int s = 0;
+  for (int i0 = 0; i0 < n_rows; i0 += ROWS, s ^= 1) {
+    const int nr = min(ROWS, n_rows - i0);
+    const bool more = i0 + ROWS < n_rows;
+    if (more) load(s ^ 1, i0 + ROWS);                         // that stage was walked two rounds ago (barrier at the loop's end)
+    if (more) ssm_cp_wait<1>(); else ssm_cp_wait<0>();
+    __syncthreads();
+    if (tid < nr) {
+      float* t = stage[s][tid] + 2 * NP + SSM_PC;
+      const float z = t[0] + bias;
+      const float dt = z > 20.f ? z + log1pf(expf(-z)) : log1pf(expf(z));
+      t[0] = dt;
+      t[1] = expf(a * dt);
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int r = 0; r < nr; ++r) {
+      const float* row = stage[s][r];
+      const float dt = row[2 * NP + SSM_PC], da = row[2 * NP + SSM_PC + 1];
+      const float2 xv = *reinterpret_cast<const float2*>(row + 2 * NP + 2 * pl);
+      const float2 u0 = make_float2(dt * xv.x, dt * xv.x), u1 = make_float2(dt * xv.y, dt * xv.y), dd = make_float2(da, da);
+      float2 a0 = make_float2(0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {                          // two states per instruction (fma.rn.f32x2)
+        const float4 b = *reinterpret_cast<const float4*>(row + 4 * (ns + SSM_NS * k));
+        const float4 c = *reinterpret_cast<const float4*>(row + NP + 4 * (ns + SSM_NS * k));
+        const float2 blo = make_float2(b.x, b.y), bhi = make_float2(b.z, b.w), clo = make_float2(c.x, c.y), chi = make_float2(c.z, c.w);
+        S0[2 * k] = __ffma2_rn(S0[2 * k], dd, __fmul2_rn(blo, u0));          a0 = __ffma2_rn(S0[2 * k], clo, a0);
+        S1[2 * k] = __ffma2_rn(S1[2 * k], dd, __fmul2_rn(blo, u1));          a1 = __ffma2_rn(S1[2 * k], clo, a1);
+        S0[2 * k + 1] = __ffma2_rn(S0[2 * k + 1], dd, __fmul2_rn(bhi, u0));  a2 = __ffma2_rn(S0[2 * k + 1], chi, a2);
+        S1[2 * k + 1] = __ffma2_rn(S1[2 * k + 1], dd, __fmul2_rn(bhi, u1));  a3 = __ffma2_rn(S1[2 * k + 1], chi, a3);
+      }
+      float acc0 = (a0.x + a0.y) + (a2.x + a2.y);
+      float acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+#pragma unroll
+      for (int o = 1; o < SSM_NS; o <<= 1) {
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+      }
+      if (ns == 0) {
+        float* yo = y + (size_t)(row0 + i0 + r) * inner + h * P + p0;
+        if (p0 < P) yo[0] = fmaf(dsk, xv.x, acc0);
+        if (p0 + 1 < P) yo[1] = fmaf(dsk, xv.y, acc1);
+      }
+    }
+    __syncthreads();                                          // everyone is done with stage s before it is loaded again
+  }
+  if (write_state) {
+#pragma unroll
+    for (int k = 0; k < K4; ++k)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = 4 * (ns + SSM_NS * k) + j;
+        const float2 v0 = S0[2 * k + (j >> 1)], v1 = S1[2 * k + (j >> 1)];
+        if (p0 < P && n < N) sp0[n] = (j & 1) ? v0.y : v0.x;
+        if (p0 + 1 < P && n < N) sp0[N + n] = (j & 1) ? v1.y : v1.x;
+      }
   }
 }
 
@@ -107,18 +180,18 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
                        const int* req_state_slot, int write_state, cudaStream_t stream) {
   if (n_reqs <= 0) return KF_OK;
   if (N < 1 || N > SSM_MAX_N || P < 1 || heads < 1 || groups < 1 || heads % groups) return KF_ERR_SIZE;
-  const dim3 grid(n_reqs * heads, kf_ceil_div(P, SSM_PC)), block(SSM_PC * SSM_NS);
-  const int nper = kf_ceil_div(N, SSM_NS);
-#define KF_GO2(NPER, TW)                                                                                              \
-  kf_launch(ssm_scan_kernel<NPER, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,    \
+  const dim3 grid(n_reqs * heads, kf_ceil_div(P, SSM_PC)), block(SSM_THREADS);
+  // 16-byte copies when every offset into the rows is a multiple of four floats
+  const int vec = (N % 4 == 0 && P % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
+#define KF_GO2(K4, ROWS, TW)                                                                                            \
+  kf_launch(ssm_scan_kernel<K4, ROWS, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,   \
             (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
-            req_state_slot, write_state)
-#define KF_GO(TW)                                    \
-  do {                                               \
-    if (nper <= 4) KF_GO2(4, TW);                    \
-    else if (nper <= 8) KF_GO2(8, TW);               \
-    else if (nper <= 16) KF_GO2(16, TW);             \
-    else KF_GO2(32, TW);                             \
+            req_state_slot, write_state, vec)
+#define KF_GO(TW)                                      \
+  do {                                                 \
+    if (N <= 64) KF_GO2(1, 16, TW);                    \
+    else if (N <= 128) KF_GO2(2, 16, TW);              \
+    else KF_GO2(4, 8, TW);                             \
   } while (0)
   if (w_dtype == KF_F32) KF_GO(float);
   else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);
