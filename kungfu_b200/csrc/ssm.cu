@@ -174,10 +174,82 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   }
 }
 
+// One row per request (decoding): nothing is staged; every thread fetches its states, its part of B and C and the row's
+// x and dt straight from global memory, all loads in flight at once.  Same split of the work and the same order of sums
+// as the walk above, so a token gives the same bits whether it came alone or in a portion.
+template <int K4, typename TW>
+__global__ void __launch_bounds__(SSM_THREADS)
+ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ proj, int ld_p, int dt_col0,
+                const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
+                float* __restrict__ state, float* __restrict__ y, int heads, int groups, int P, int N,
+                int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
+                const int* __restrict__ req_state_slot, int write_state) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int req = blockIdx.x / heads, h = blockIdx.x - req * heads;
+  if (req >= n_reqs || req_n_rows[req] <= 0) return;
+  const int t = req_row_start[req], slot = req_state_slot[req];
+  const int g = h / (heads / groups);
+  const int inner = heads * P;
+  const int tid = threadIdx.x, ns = tid & (SSM_NS - 1), pl = tid / SSM_NS;
+  const int p0 = blockIdx.y * SSM_PC + 2 * pl;
+  const float* row = xbc + (size_t)t * ld_x;
+  float* sp0 = state + (((size_t)slot * heads + h) * P + p0) * N;
+  float2 S0[2 * K4], S1[2 * K4], bb[2 * K4], cc[2 * K4];
+#pragma unroll
+  for (int k = 0; k < K4; ++k)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = 4 * (ns + SSM_NS * k) + j;
+      const bool in = n < N;
+      const float v0 = (p0 < P && in) ? sp0[n] : 0.f, v1 = (p0 + 1 < P && in) ? sp0[N + n] : 0.f;
+      const float b = in ? row[inner + g * N + n] : 0.f, c = in ? row[inner + (groups + g) * N + n] : 0.f;
+      if (j & 1) { S0[2 * k + (j >> 1)].y = v0; S1[2 * k + (j >> 1)].y = v1; bb[2 * k + (j >> 1)].y = b; cc[2 * k + (j >> 1)].y = c; }
+      else { S0[2 * k + (j >> 1)].x = v0; S1[2 * k + (j >> 1)].x = v1; bb[2 * k + (j >> 1)].x = b; cc[2 * k + (j >> 1)].x = c; }
+    }
+  const float x0 = p0 < P ? row[h * P + p0] : 0.f, x1 = p0 + 1 < P ? row[h * P + p0 + 1] : 0.f;
+  const float z = proj[(size_t)t * ld_p + dt_col0 + h] + kf_load(dt_bias, h);
+  const float dt = z > 20.f ? z + log1pf(expf(-z)) : log1pf(expf(z));
+  const float da = expf(-expf(kf_load(a_log, h)) * dt);
+  const float2 u0 = make_float2(dt * x0, dt * x0), u1 = make_float2(dt * x1, dt * x1), dd = make_float2(da, da);
+  float2 a0 = make_float2(0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+#pragma unroll
+  for (int k = 0; k < K4; ++k) {
+    S0[2 * k] = __ffma2_rn(S0[2 * k], dd, __fmul2_rn(bb[2 * k], u0));              a0 = __ffma2_rn(S0[2 * k], cc[2 * k], a0);
+    S1[2 * k] = __ffma2_rn(S1[2 * k], dd, __fmul2_rn(bb[2 * k], u1));              a1 = __ffma2_rn(S1[2 * k], cc[2 * k], a1);
+    S0[2 * k + 1] = __ffma2_rn(S0[2 * k + 1], dd, __fmul2_rn(bb[2 * k + 1], u0));  a2 = __ffma2_rn(S0[2 * k + 1], cc[2 * k + 1], a2);
+    S1[2 * k + 1] = __ffma2_rn(S1[2 * k + 1], dd, __fmul2_rn(bb[2 * k + 1], u1));  a3 = __ffma2_rn(S1[2 * k + 1], cc[2 * k + 1], a3);
+  }
+  float acc0 = (a0.x + a0.y) + (a2.x + a2.y);
+  float acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+#pragma unroll
+  for (int o = 1; o < SSM_NS; o <<= 1) {
+    acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+    acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+  }
+  if (ns == 0) {
+    const float dsk = kf_load(d_skip, h);
+    float* yo = y + (size_t)t * inner + h * P + p0;
+    if (p0 < P) yo[0] = fmaf(dsk, x0, acc0);
+    if (p0 + 1 < P) yo[1] = fmaf(dsk, x1, acc1);
+  }
+  if (write_state) {
+#pragma unroll
+    for (int k = 0; k < K4; ++k)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = 4 * (ns + SSM_NS * k) + j;
+        const float2 v0 = S0[2 * k + (j >> 1)], v1 = S1[2 * k + (j >> 1)];
+        if (p0 < P && n < N) sp0[n] = (j & 1) ? v0.y : v0.x;
+        if (p0 + 1 < P && n < N) sp0[N + n] = (j & 1) ? v1.y : v1.x;
+      }
+  }
+}
+
 KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, int dt_col0, const void* dt_bias,
                        const void* a_log, const void* d_skip, int w_dtype, float* state, float* y, int heads, int groups,
                        int P, int N, int n_reqs, const int* req_row_start, const int* req_n_rows,
-                       const int* req_state_slot, int write_state, cudaStream_t stream) {
+                       const int* req_state_slot, int write_state, int single_rows, cudaStream_t stream) {
   if (n_reqs <= 0) return KF_OK;
   if (N < 1 || N > SSM_MAX_N || P < 1 || heads < 1 || groups < 1 || heads % groups) return KF_ERR_SIZE;
   const dim3 grid(n_reqs * heads, kf_ceil_div(P, SSM_PC)), block(SSM_THREADS);
@@ -187,8 +259,17 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
   kf_launch(ssm_scan_kernel<K4, ROWS, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,   \
             (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
             req_state_slot, write_state, vec)
+#define KF_STEP(K4, TW)                                                                                                 \
+  kf_launch(ssm_step_kernel<K4, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,         \
+            (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
+            req_state_slot, write_state)
 #define KF_GO(TW)                                      \
   do {                                                 \
+    if (single_rows) {                                 \
+      if (N <= 64) KF_STEP(1, TW);                     \
+      else if (N <= 128) KF_STEP(2, TW);               \
+      else KF_STEP(4, TW);                             \
+    } else                                             \
     if (N <= 64) KF_GO2(1, 16, TW);                    \
     else if (N <= 128) KF_GO2(2, 16, TW);              \
     else KF_GO2(4, 8, TW);                             \
@@ -198,6 +279,7 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
   else return KF_ERR_DTYPE;
 #undef KF_GO
 #undef KF_GO2
+#undef KF_STEP
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

@@ -539,15 +539,19 @@ _CONV_ACT = {None: 0, "none": 0, "silu": 1}
 
 
 @_dispatch("short_conv")
-def short_conv(proj, col0: int, in_bias, weight, out_bias, act, state, out, ctx) -> None:
+def short_conv(proj, col0: int, in_bias, weight, out_bias, act, state, out, ctx, commit_inline: bool = False) -> bool:
     """out[t, c] = act(sum_j weight[c, j] * u_(t - taps + 1 + j)[c] + out_bias[c]) over the rows of every request of the step,
     u = proj[:, col0 + c] + in_bias[c]; rows before the step come from `state` [requests, taps - 1, C] (32-bit), zeros
-    before the sequence's start.  `proj` and `out` are 32-bit."""
+    before the sequence's start.  `proj` and `out` are 32-bit.
+    `commit_inline` (only for steps in which no request has more than one row): the kernel also moves the state on.
+    Returns whether it did; if not, `short_conv_commit` has to run after every reader of the old state."""
     T = out.shape[0]
     C, taps = weight.shape
+    inline = bool(commit_inline) and taps > 1
     _check(library().kf_short_conv(_p(proj), proj.shape[1], int(col0), _p(in_bias), _p(weight), _p(out_bias), _dt(weight), C,
                                    taps, _CONV_ACT[act], _p(state), _p(out), out.shape[1], _p(ctx.row_req),
-                                   _p(ctx.req_row_start), _p(ctx.req_state_slot), T, _stream()), "short_conv")
+                                   _p(ctx.req_row_start), _p(ctx.req_state_slot), T, int(inline), _stream()), "short_conv")
+    return inline
 
 
 @_dispatch("short_conv_commit")
@@ -563,10 +567,13 @@ def short_conv_commit(proj, col0: int, in_bias, n_channels: int, taps: int, stat
 
 @_dispatch("qkv_prepare")
 def qkv_prepare(proj, col0: int, in_bias, conv_w, conv_state, q_norm, k_norm, eps: float, cos, sin, rot: int,
-                interleaved: bool, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, ctx, cache, q_out) -> None:
+                interleaved: bool, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, ctx, cache, q_out,
+                commit_inline: bool = False) -> bool:
     """From the 32-bit q|k|v projection to the attention's operands: optional bias, short convolution (reading
     `conv_state`), per-head RMS norm of q and k, rotation (interleaved pairs or halves), q into `q_out`
-    [T, n_heads * D] and k, v into the pages of `cache`, D = the pages' head size, tails zero."""
+    [T, n_heads * D] and k, v into the pages of `cache`, D = the pages' head size, tails zero.
+    `commit_inline` (only for steps in which no request has more than one row): the kernel also moves the convolution's
+    state on, when its sizes allow.  Returns whether it did; if not, `short_conv_commit` has to run afterwards."""
     T = q_out.shape[0]
     D = cache.pages.shape[-1]
     if q_out.shape[1] != n_heads * D:
@@ -577,12 +584,15 @@ def qkv_prepare(proj, col0: int, in_bias, conv_w, conv_state, q_norm, k_norm, ep
     for w in (in_bias, q_norm, k_norm):
         if w is not None and _dt(w) != wdt:
             raise KernelError("qkv_prepare: bias, convolution and norm weights must share one element type")
+    inline = bool(commit_inline and conv_w is not None and taps > 1 and conv_state is not None and
+                  library().kf_qkv_prepare_commits_inline(proj.shape[1], int(col0), int(rot), int(interleaved), key_dim, value_dim, D))
     _check(library().kf_qkv_prepare(_p(proj), proj.shape[1], int(col0), _p(in_bias), _p(conv_w), taps, _p(conv_state),
                                     _p(q_norm), _p(k_norm), wdt, _f(eps), _p(cos), _p(sin), int(rot), int(interleaved),
                                     n_heads, n_kv_heads, key_dim, value_dim, D, _p(ctx.positions), _p(ctx.row_req),
                                     _p(ctx.req_row_start), _p(ctx.req_state_slot), _p(table), table.shape[1],
                                     cache.page_size, _p(cache.pages), _dt(cache.pages), _p(q_out), _dt(q_out),
-                                    int(cache.writes), T, _stream()), "qkv_prepare")
+                                    int(cache.writes), T, int(inline), _stream()), "qkv_prepare")
+    return inline
 
 
 @_dispatch("head_gate")
@@ -602,7 +612,7 @@ def ssm_scan(xbc, proj, dt_col0: int, dt_bias, a_log, d_skip, state, y, heads: i
     _check(library().kf_ssm_scan(_p(xbc), xbc.shape[1], _p(proj), proj.shape[1], int(dt_col0), _p(dt_bias), _p(a_log),
                                  _p(d_skip), _dt(a_log), _p(state), _p(y), heads, groups, head_dim, state_dim, ctx.n_reqs,
                                  _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes),
-                                 _stream()), "ssm_scan")
+                                 int(bool(getattr(ctx, "decode_only", False))), _stream()), "ssm_scan")
 
 
 @_dispatch("gated_group_norm")

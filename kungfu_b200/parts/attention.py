@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FixedState, Mixer, PagedKV, PositionEncoding, StateBundle, register_mixer
+from .base import FixedState, Mixer, PagedKV, PositionEncoding, StateBundle, pad_rows, register_mixer
 from .conv import ShortConv
 
 
@@ -105,6 +105,8 @@ class ConvGatedAttention(Mixer):
         self.width = wo.shape[0]
         if w_in.numel() and w_in.shape[0] != self.proj_width:
             raise ValueError(f"stacked projection has shape {tuple(w_in.shape)}, expected {self.proj_width} rows")
+        self.w_in = pad_rows(w_in)                          # result rows start on 16-byte boundaries
+        self.proj_width = max(self.proj_width, self.w_in.shape[0])
         if conv is not None and conv.channels != self.qkv_width:
             raise ValueError(f"the convolution has {conv.channels} channels, q|k|v have {self.qkv_width}")
         rot = getattr(position, "rotary_dims", 0) if position is not None else 0
@@ -132,10 +134,11 @@ class ConvGatedAttention(Mixer):
             rot, interleaved = 0, False
         q = ctx.buf("attn_q", (T, nh * D), ctx.act_dtype)
         conv = self.conv
-        ops.qkv_prepare(proj, 0, self.bias, conv.weight if conv else None, tail.state if tail is not None else None,
-                        self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, nh, nkv, self.key_dim,
-                        self.value_dim, ctx, kv, q)
-        if tail is not None:
+        moves = tail is not None and tail.writes
+        done = ops.qkv_prepare(proj, 0, self.bias, conv.weight if conv else None, tail.state if tail is not None else None,
+                               self.q_norm, self.k_norm, self.norm_eps, cos, sin, rot, interleaved, nh, nkv, self.key_dim,
+                               self.value_dim, ctx, kv, q, commit_inline=moves and bool(getattr(ctx, "decode_only", False)))
+        if moves and not done:
             conv.commit(proj, 0, self.bias, ctx, tail)
         o = ctx.buf("attn_o", (T, nh * D), ctx.act_dtype)
         ops.paged_attention(q, o, ctx, kv, nh, nkv, D, self.scale, self.softcap, self.window)

@@ -48,6 +48,15 @@ class StateBundle:
 StateNeed = PagedKV | FixedState | StateBundle
 
 
+def pad_rows(w: torch.Tensor, multiple: int = 4) -> torch.Tensor:
+    """`w` with zero rows appended until its row count is a multiple of `multiple`: a projection whose 32-bit result
+    then has rows that start on 16-byte boundaries, which the kernels that read it in 16-byte vectors want."""
+    extra = (-w.shape[0]) % multiple
+    if extra == 0 or w.numel() == 0:
+        return w
+    return torch.cat([w, torch.zeros((extra, *w.shape[1:]), dtype=w.dtype, device=w.device)], dim=0).contiguous()
+
+
 # ---- part kinds -----------------------------------------------------------------------------------
 
 class Part:

@@ -31,9 +31,14 @@ class ShortConv(Part):
         return FixedState((max(self.taps - 1, 1), self.channels), torch.float32)
 
     def forward(self, proj, col0: int, in_bias, ctx, state_view, tag: str = "conv_out") -> torch.Tensor:
-        """32-bit [rows, channels]: the convolution of columns col0.. of `proj` (+ in_bias) over each request's rows."""
+        """32-bit [rows, channels]: the convolution of columns col0.. of `proj` (+ in_bias) over each request's rows; the
+        state is moved on to the end of the step's rows (in the same kernel when no request has more than one row)."""
         out = ctx.buf(tag, (proj.shape[0], self.channels), torch.float32)
-        ops.short_conv(proj, col0, in_bias, self.weight, self.bias, self.activation, state_view.state, out, ctx)
+        inline = state_view.writes and bool(getattr(ctx, "decode_only", False))
+        done = ops.short_conv(proj, col0, in_bias, self.weight, self.bias, self.activation, state_view.state, out, ctx,
+                              commit_inline=inline)
+        if not done:
+            self.commit(proj, col0, in_bias, ctx, state_view)
         return out
 
     def commit(self, proj, col0: int, in_bias, ctx, state_view) -> None:

@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FixedState, Mixer, StateBundle, register_mixer
+from .base import FixedState, Mixer, StateBundle, pad_rows, register_mixer
 from .conv import ShortConv
 
 
@@ -32,6 +32,10 @@ class Mamba2Mixer(Mixer):
         self.conv_width = self.inner + 2 * self.groups * self.state_dim
         self.proj_width = self.inner + self.conv_width + self.heads
         self.width = wo.shape[0]
+        if w_in.numel() and w_in.shape[0] != self.proj_width:
+            raise ValueError(f"the input projection has {w_in.shape[0]} rows, expected {self.proj_width}")
+        self.w_in = pad_rows(w_in)                          # result rows start on 16-byte boundaries
+        self.proj_width = max(self.proj_width, self.w_in.shape[0])
         if self.heads % self.groups:
             raise ValueError(f"heads {self.heads} is not a multiple of groups {self.groups}")
         if self.inner % self.norm_groups:
@@ -49,8 +53,7 @@ class Mamba2Mixer(Mixer):
         T = x.shape[0]
         proj = ctx.buf("ssm_proj", (T, self.proj_width), torch.float32)
         ops.linear(x, self.w_in, proj)
-        xbc = self.conv.forward(proj, self.inner, None, ctx, tail, tag="ssm_xbc")
-        self.conv.commit(proj, self.inner, None, ctx, tail)
+        xbc = self.conv.forward(proj, self.inner, None, ctx, tail, tag="ssm_xbc")        # also moves the tail on
         y = ctx.buf("ssm_y", (T, self.inner), torch.float32)
         ops.ssm_scan(xbc, proj, self.inner + self.conv_width, self.dt_bias, self.a_log, self.d_skip, memory.state, y,
                      self.heads, self.groups, self.head_dim, self.state_dim, ctx, writes=memory.writes)

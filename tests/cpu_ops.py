@@ -125,7 +125,7 @@ class CpuOps:
         old = state[slot, :taps - 1].float() if (state is not None and taps > 1) else torch.zeros(0, C)
         return torch.cat([old, u], 0), r0, n, slot
 
-    def short_conv(self, proj, col0, in_bias, weight, out_bias, act, state, out, ctx):
+    def short_conv(self, proj, col0, in_bias, weight, out_bias, act, state, out, ctx, commit_inline=False):
         C, taps = weight.shape
         for req in range(ctx.n_reqs):
             if int(ctx.req_n_rows[req]) <= 0:
@@ -139,6 +139,7 @@ class CpuOps:
             if act == "silu":
                 y = y * torch.sigmoid(y)
             out[r0:r0 + n] = y
+        return False                                   # the state is never moved on here: the caller runs the commit
 
     def short_conv_commit(self, proj, col0, in_bias, n_channels, taps, state, ctx, w_dtype=None):
         if taps <= 1:
@@ -150,7 +151,7 @@ class CpuOps:
             state[slot, :taps - 1] = u[-(taps - 1):]
 
     def qkv_prepare(self, proj, col0, in_bias, conv_w, conv_state, q_norm, k_norm, eps, cos, sin, rot, interleaved,
-                    nh, nkv, dk, dv, ctx, cache, q_out):
+                    nh, nkv, dk, dv, ctx, cache, q_out, commit_inline=False):
         T = q_out.shape[0]
         D = cache.pages.shape[-1]
         C = (nh + nkv) * dk + nkv * dv
@@ -182,7 +183,7 @@ class CpuOps:
         qp[~valid] = 0
         q_out.copy_(qp.reshape(T, nh * D).to(q_out.dtype))
         if not cache.writes:
-            return
+            return False
         table = ctx.block_tables[cache.group]
         P = cache.page_size
         for t in range(T):
@@ -195,6 +196,7 @@ class CpuOps:
             cache.pages[page, :, :, pos % P, :] = 0
             cache.pages[page, 0, :, pos % P, :dk] = k[t].to(cache.pages.dtype)
             cache.pages[page, 1, :, pos % P, :dv] = v[t].to(cache.pages.dtype)
+        return False
 
     def head_gate(self, o, proj, gate_col0, nh, dv, D, out, ctx):
         T = out.shape[0]

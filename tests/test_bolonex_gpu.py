@@ -251,6 +251,51 @@ def test_state_space_scan_in_portions(wdtype, heads, groups, P, N):
     assert float(state[1].min()) == 3.0 and float(y[-1].min()) == 5.0
 
 
+@pytest.mark.parametrize("heads,groups,P,N,taps", [(2, 1, 16, 16, 3), (6, 3, 8, 40, 4), (4, 2, 64, 128, 4), (3, 1, 12, 10, 2)])
+def test_steps_of_single_rows_token_by_token(heads, groups, P, N, taps):
+    """Decoding: every request brings one row, and the kernels then take other paths (the convolution moves its own
+    tail on, the recurrence fetches its operands without staging).  Three requests, twelve steps, against the plain
+    recurrence and convolution over each request's whole history."""
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(heads + N)
+    inner = heads * P
+    C = inner + 2 * groups * N
+    ld_p = -(-(inner + C + heads) // 4) * 4
+    steps, n_req = 12, 3
+    w = (0.5 * torch.randn(C, taps, generator=g))
+    bias = 0.2 * torch.randn(C, generator=g)
+    a_log = -3.0 + 2.5 * torch.rand(heads, generator=g)
+    dt_bias, d_skip = 0.5 * torch.randn(heads, generator=g), torch.randn(heads, generator=g)
+    hist = torch.randn(n_req, steps, ld_p, generator=g)
+    conv_state = torch.zeros(4, max(taps - 1, 1), C, device=DEV)
+    memory = torch.zeros(4, heads, P, N, device=DEV)
+    ys = torch.empty(n_req, steps, inner)
+    for i in range(steps):
+        st = FakeStep(rows=(1, 1, 1), before=(i, i, i), slots=(3, 0, 2))
+        st.decode_only = True
+        proj = torch.zeros(st.n_rows, ld_p)
+        proj[:n_req] = hist[:, i]
+        proj = proj.to(DEV)
+        xbc = torch.empty(st.n_rows, C, device=DEV)
+        assert ops.short_conv(proj, inner, None, w.to(DEV), bias.to(DEV), "silu", conv_state, xbc, st, commit_inline=True) == (taps > 1)
+        y = torch.empty(st.n_rows, inner, device=DEV)
+        ops.ssm_scan(xbc, proj, inner + C, dt_bias.to(DEV), a_log.to(DEV), d_skip.to(DEV), memory, y, heads, groups, P, N, st)
+        ys[:, i] = y[:n_req].cpu()
+    for r in range(n_req):
+        x = pb.silu(pb.short_conv(hist[r][:, inner:inner + C].double(), w, bias))
+        dt = pb.softplus(hist[r][:, inner + C:inner + C + heads].double() + dt_bias.double())
+        A = -torch.exp(a_log.double())
+        for h in range(heads):
+            gi = h // (heads // groups)
+            S = torch.zeros(N, P, dtype=torch.float64)
+            for i in range(steps):
+                xs, B = x[i, h * P:(h + 1) * P], x[i, inner + gi * N:inner + (gi + 1) * N]
+                Cc = x[i, inner + groups * N + gi * N:inner + groups * N + (gi + 1) * N]
+                S = torch.exp(A[h] * dt[i, h]) * S + dt[i, h] * torch.outer(B, xs)
+                ref = S.T @ Cc + d_skip[h].double() * xs
+                assert _rel(ys[r, i, h * P:(h + 1) * P], ref) < 5e-5, (r, h, i)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("inner,parts", [(32, 1), (48, 2), (36, 3), (512, 2), (4096, 4)])
 def test_gated_group_norm(dtype, inner, parts):
