@@ -65,7 +65,13 @@ BX_E = config(512, 3000, [layer("attention", attention(4, 2, 128, 128, 4, 0.09, 
                                                       scaling={"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}),
                                 1024, weights_of=0)], scale=3.0)
 
-CASES = {"A": (BX_A, [5, 17, 23, 40, 11, 30], 4), "B": (BX_B, [1, 31, 40, 70, 9, 50], 8), "C": (BX_C, [3, 50, 64, 29, 77, 2], 16)}
+# the smallest of everything: one tap (the "convolution" is a scale per channel and keeps no tail), no rotation, odd head
+# sizes (keys of 6, values of 7, so heads of 8 in the cache), one state-space head of 5 with 7 states, one layer of each
+BX_D = config(24, 50, [layer("attention", attention(2, 1, 6, 7, 1, 0.4), 40), layer("mamba2", mamba2(1, 5, 7, 1, 1, 1), None),
+                       layer("mamba2", mamba2(3, 5, 9, 1, 3, 2), 16)], scale=1.0)
+
+CASES = {"A": (BX_A, [5, 17, 23, 40, 11, 30], 4), "B": (BX_B, [1, 31, 40, 70, 9, 50], 8), "C": (BX_C, [3, 50, 64, 29, 77, 2], 16),
+         "D": (BX_D, [4, 19, 1, 33, 8, 12], 4)}
 
 
 def draw_tensors(cfg_dict: dict, seed: int, sharp: bool = False) -> dict:

@@ -105,7 +105,7 @@ def models(tmp_path_factory):
     return out
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 def test_cpu_modes_match_plain(models, cpu_ops, name, mode):
     folder, cfg, reqs, ref, page = models[name]
