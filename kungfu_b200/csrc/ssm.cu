@@ -10,20 +10,22 @@
 // The tokens of a request are walked in order, whatever the step holds of it (one token, a portion, a whole prompt),
 // so the result at a token does not depend on how the sequence was cut.
 //
-// Work split: a block of 256 threads owns (request, head, 32 values of p).  Thread (pl, ns) keeps S[n][p] for two values
-// of p and every n whose group of four, n / 4, is ns modulo 16: up to 32 numbers in registers; the sixteen lanes that
-// share a pair of p add their partial sums of S^T C by shuffles.  (With eight lanes per pair and twice the registers a
-// block had four warps, one per scheduler, and issued one instruction in four cycles: every wait on shared memory or on
-// the multiply-add before it stood exposed.)  Rows are staged in shared memory, B, C, x and dt as
-// they stand in global memory, by 4-byte cp.async into a ring of two stages, so that the next rows arrive while the
-// current ones are walked; the walk itself reads 16-byte vectors (sixteen neighbouring lanes read 256 contiguous bytes)
-// and issues three packed instructions (fma.rn.f32x2: two neighbouring states each) per pair of states and no global load.  Shared rows are padded with zeros to a
-// multiple of 64 states: padded states stay zero and add nothing, so the walk has no bounds checks.
+// Work split: a block of 128 threads owns (request, head, 32 values of p).  Thread (pl, ns) keeps S[n][p] for two values
+// of p and every n whose group of four, n / 4, is ns modulo 8: up to 64 numbers in registers, as pairs of neighbouring
+// states that one packed instruction (fma.rn.f32x2) updates together; the eight lanes that share a pair of columns add
+// their partial sums of S^T C by shuffles (odd lanes take one column, even lanes the other, after the first exchange).
+// Rows are staged in shared memory, B, C, x and dt as they stand in global memory, by cp.async (16 bytes where offsets
+// allow, else 4) into a ring of two stages, so that the next rows arrive while the current ones are walked; the walk reads
+// 16-byte vectors (eight neighbouring lanes read 128 contiguous bytes) and issues three packed instructions per pair of
+// states and no global load.  Shared rows are padded with zeros to a multiple of 32 states: padded states stay zero and
+// add nothing, so the walk has no bounds checks.  (Sixteen lanes per column pair, i.e. twice the warps with half the
+// states each, walk one prompt no faster and several prompts a quarter slower: the work per row that does not shrink
+// with the tile, shared loads, shuffles and address arithmetic, is then paid twice.)
 // State layout: state[slot][head][p][n], n fastest.
 #include "common.cuh"
 
 constexpr int SSM_PC = 32;        // values of p per block
-constexpr int SSM_NS = 16;        // lanes that share a pair of p
+constexpr int SSM_NS = 8;         // lanes that share a pair of p
 constexpr int SSM_THREADS = (SSM_PC / 2) * SSM_NS;
 constexpr int SSM_MAX_N = 256;
 
@@ -40,7 +42,7 @@ template <int N> __device__ __forceinline__ void ssm_cp_wait() { asm volatile("c
 
 // K4: groups of four states per thread (the padded state size is 64 * K4); ROWS: rows per stage.
 template <int K4, int ROWS, typename TW>
-__global__ void __launch_bounds__(SSM_THREADS, 2)
+__global__ void __launch_bounds__(SSM_THREADS, 4)
 ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ proj, int ld_p, int dt_col0,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, float* __restrict__ y, int heads, int groups, int P, int N,
@@ -48,7 +50,6 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
                 const int* __restrict__ req_state_slot, int write_state, int vec) {
   constexpr int NP = 4 * SSM_NS * K4;                         // padded state size
   constexpr int ROW_F = 2 * NP + SSM_PC + 4;                  // floats of one staged row: B | C | x | dt, decay, -, -
-  kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ __align__(16) float stage[2][ROWS][ROW_F];
   const int req = blockIdx.x / heads, h = blockIdx.x - req * heads;
@@ -115,6 +116,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
 
   load(0, 0);
   int s = 0;
+  float* yo = y + (size_t)row0 * inner + h * P + p0 + (ns & 1);          // where lane ns < 2 stores column p0 + ns
   for (int i0 = 0; i0 < n_rows; i0 += ROWS, s ^= 1) {
     const int nr = min(ROWS, n_rows - i0);
     const bool more = i0 + ROWS < n_rows;
@@ -146,21 +148,21 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
         S0[2 * k + 1] = __ffma2_rn(S0[2 * k + 1], dd, __fmul2_rn(bhi, u0));  a2 = __ffma2_rn(S0[2 * k + 1], chi, a2);
         S1[2 * k + 1] = __ffma2_rn(S1[2 * k + 1], dd, __fmul2_rn(bhi, u1));  a3 = __ffma2_rn(S1[2 * k + 1], chi, a3);
       }
-      float acc0 = (a0.x + a0.y) + (a2.x + a2.y);
-      float acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+      const float acc0 = (a0.x + a0.y) + (a2.x + a2.y), acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+      // the sum over the lanes of a pair of columns: odd lanes take over the second column, even lanes the first, then
+      // one value per lane goes through the remaining steps
+      float v = ((ns & 1) ? acc1 : acc0) + __shfl_xor_sync(0xffffffffu, (ns & 1) ? acc0 : acc1, 1);
 #pragma unroll
-      for (int o = 1; o < SSM_NS; o <<= 1) {
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
-      }
-      if (ns == 0) {
-        float* yo = y + (size_t)(row0 + i0 + r) * inner + h * P + p0;
-        if (p0 < P) yo[0] = fmaf(dsk, xv.x, acc0);
-        if (p0 + 1 < P) yo[1] = fmaf(dsk, xv.y, acc1);
-      }
+      for (int o = 2; o < SSM_NS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (ns < 2 && p0 + ns < P) yo[(size_t)r * inner] = fmaf(dsk, ns ? xv.y : xv.x, v);
     }
+    yo += (size_t)nr * inner;
     __syncthreads();                                          // everyone is done with stage s before it is loaded again
   }
+  // Dependents are let in only now: this kernel runs for hundreds of microseconds with one to four blocks per SM, and a
+  // dependent grid released at its start parks its blocks on every SM for all that time (measured on the 8-layer step:
+  // 13.9 ms against 11.7 ms when every launch waits for the one before it).
+  kf_pdl_trigger();
   if (write_state) {
 #pragma unroll
     for (int k = 0; k < K4; ++k)
@@ -220,19 +222,11 @@ ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
     S0[2 * k + 1] = __ffma2_rn(S0[2 * k + 1], dd, __fmul2_rn(bb[2 * k + 1], u0));  a2 = __ffma2_rn(S0[2 * k + 1], cc[2 * k + 1], a2);
     S1[2 * k + 1] = __ffma2_rn(S1[2 * k + 1], dd, __fmul2_rn(bb[2 * k + 1], u1));  a3 = __ffma2_rn(S1[2 * k + 1], cc[2 * k + 1], a3);
   }
-  float acc0 = (a0.x + a0.y) + (a2.x + a2.y);
-  float acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+  const float acc0 = (a0.x + a0.y) + (a2.x + a2.y), acc1 = (a1.x + a1.y) + (a3.x + a3.y);
+  float v = ((ns & 1) ? acc1 : acc0) + __shfl_xor_sync(0xffffffffu, (ns & 1) ? acc0 : acc1, 1);
 #pragma unroll
-  for (int o = 1; o < SSM_NS; o <<= 1) {
-    acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
-    acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
-  }
-  if (ns == 0) {
-    const float dsk = kf_load(d_skip, h);
-    float* yo = y + (size_t)t * inner + h * P + p0;
-    if (p0 < P) yo[0] = fmaf(dsk, x0, acc0);
-    if (p0 + 1 < P) yo[1] = fmaf(dsk, x1, acc1);
-  }
+  for (int o = 2; o < SSM_NS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (ns < 2 && p0 + ns < P) y[(size_t)t * inner + h * P + p0 + ns] = fmaf(kf_load(d_skip, h), ns ? x1 : x0, v);
   if (write_state) {
 #pragma unroll
     for (int k = 0; k < K4; ++k)
@@ -255,8 +249,11 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
   const dim3 grid(n_reqs * heads, kf_ceil_div(P, SSM_PC)), block(SSM_THREADS);
   // 16-byte copies when every offset into the rows is a multiple of four floats
   const int vec = (N % 4 == 0 && P % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
+// The staged walk is launched WITHOUT the programmatic-dependent-launch attribute: released early by its predecessor,
+// its blocks (37 KB of shared memory and a quarter of an SM's registers each) would sit on every SM waiting while the
+// kernels before it still need the room; measured on an 8-layer prompt step, 8.3 ms with the attribute, 6.5 ms without.
 #define KF_GO2(K4, ROWS, TW)                                                                                            \
-  kf_launch(ssm_scan_kernel<K4, ROWS, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,   \
+  ssm_scan_kernel<K4, ROWS, TW><<<grid, block, 0, stream>>>(xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,          \
             (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
             req_state_slot, write_state, vec)
 #define KF_STEP(K4, TW)                                                                                                 \
@@ -266,13 +263,15 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
 #define KF_GO(TW)                                      \
   do {                                                 \
     if (single_rows) {                                 \
-      if (N <= 64) KF_STEP(1, TW);                     \
-      else if (N <= 128) KF_STEP(2, TW);               \
-      else KF_STEP(4, TW);                             \
+      if (N <= 32) KF_STEP(1, TW);                     \
+      else if (N <= 64) KF_STEP(2, TW);                \
+      else if (N <= 128) KF_STEP(4, TW);               \
+      else KF_STEP(8, TW);                             \
     } else                                             \
-    if (N <= 64) KF_GO2(1, 16, TW);                    \
-    else if (N <= 128) KF_GO2(2, 16, TW);              \
-    else KF_GO2(4, 8, TW);                             \
+    if (N <= 32) KF_GO2(1, 16, TW);                    \
+    else if (N <= 64) KF_GO2(2, 16, TW);               \
+    else if (N <= 128) KF_GO2(4, 16, TW);              \
+    else KF_GO2(8, 8, TW);                             \
   } while (0)
   if (w_dtype == KF_F32) KF_GO(float);
   else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);
