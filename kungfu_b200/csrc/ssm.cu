@@ -40,14 +40,19 @@ __device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
 }
 template <int N> __device__ __forceinline__ void ssm_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// K4: groups of four states per thread (the padded state size is 64 * K4); ROWS: rows per stage.
-template <int K4, int ROWS, typename TW>
+// K4: groups of four states per thread (the padded state size is 32 * K4); ROWS: rows per stage.
+// STATE_ONLY: the walk of a chunk of a long prompt from a zero state, which leaves only the chunk's end state and the
+// product of its decays (no C, no sums, no y); see kf_ssm_scan_chunked.
+// A request (or chunk) r reads its first state from state_in[slot_in[r]] and leaves its last state in
+// state_out[slot_out[r]] (slot_out[r] < 0: nowhere).
+template <int K4, int ROWS, typename TW, bool STATE_ONLY>
 __global__ void __launch_bounds__(SSM_THREADS, 4)
 ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ proj, int ld_p, int dt_col0,
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
-                float* __restrict__ state, float* __restrict__ y, int heads, int groups, int P, int N,
-                int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
-                const int* __restrict__ req_state_slot, int write_state, int vec) {
+                const float* __restrict__ state_in, const int* __restrict__ slot_in, float* __restrict__ state_out,
+                const int* __restrict__ slot_out, float* __restrict__ decay_out, float* __restrict__ y, int heads, int groups,
+                int P, int N, int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
+                int write_state, int vec) {
   constexpr int NP = 4 * SSM_NS * K4;                         // padded state size
   constexpr int ROW_F = 2 * NP + SSM_PC + 4;                  // floats of one staged row: B | C | x | dt, decay, -, -
   kf_pdl_wait();
@@ -56,7 +61,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   if (req >= n_reqs) return;
   const int n_rows = req_n_rows[req];
   if (n_rows <= 0) return;                                   // a request slot of a padded layout
-  const int row0 = req_row_start[req], slot = req_state_slot[req];
+  const int row0 = req_row_start[req];
   const int g = h / (heads / groups);
   const int inner = heads * P;
   const int tid = threadIdx.x, ns = tid & (SSM_NS - 1), pl = tid / SSM_NS;
@@ -73,13 +78,13 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
     else dst[2 * NP + px + j - 2 * pad_n] = 0.f;
   }
   float2 S0[2 * K4], S1[2 * K4];                               // pairs of neighbouring states, for p0 and p0 + 1
-  float* sp0 = state + (((size_t)slot * heads + h) * P + p0) * N;
+  const float* sp0 = STATE_ONLY ? nullptr : state_in + (((size_t)slot_in[req] * heads + h) * P + p0) * N;
 #pragma unroll
   for (int k = 0; k < K4; ++k)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = 4 * (ns + SSM_NS * k) + j;
-      const float v0 = (p0 < P && n < N) ? sp0[n] : 0.f, v1 = (p0 + 1 < P && n < N) ? sp0[N + n] : 0.f;
+      const float v0 = (!STATE_ONLY && p0 < P && n < N) ? sp0[n] : 0.f, v1 = (!STATE_ONLY && p0 + 1 < P && n < N) ? sp0[N + n] : 0.f;
       if (j & 1) { S0[2 * k + (j >> 1)].y = v0; S1[2 * k + (j >> 1)].y = v1; }
       else { S0[2 * k + (j >> 1)].x = v0; S1[2 * k + (j >> 1)].x = v1; }
     }
@@ -95,7 +100,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
         const float* row = xbc + (size_t)(row0 + i0 + r) * ld_x;
         float* dst = stage[s][r];
         if (it < nq) ssm_cp16(dst + 4 * it, row + inner + g * N + 4 * it);
-        else if (it < 2 * nq) ssm_cp16(dst + NP + 4 * (it - nq), row + inner + (groups + g) * N + 4 * (it - nq));
+        else if (it < 2 * nq) { if (!STATE_ONLY) ssm_cp16(dst + NP + 4 * (it - nq), row + inner + (groups + g) * N + 4 * (it - nq)); }
         else if (it < 2 * nq + xq) ssm_cp16(dst + 2 * NP + 4 * (it - 2 * nq), row + h * P + pbase + 4 * (it - 2 * nq));
         else ssm_cp4(dst + 2 * NP + SSM_PC, proj + (size_t)(row0 + i0 + r) * ld_p + dt_col0 + h);
       }
@@ -105,7 +110,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
         float* dst = stage[s][r];
         for (int n = tid; n < N; n += SSM_THREADS) {
           ssm_cp4(dst + n, row + inner + g * N + n);
-          ssm_cp4(dst + NP + n, row + inner + (groups + g) * N + n);
+          if (!STATE_ONLY) ssm_cp4(dst + NP + n, row + inner + (groups + g) * N + n);
         }
         if (tid < SSM_PC && pbase + tid < P) ssm_cp4(dst + 2 * NP + tid, row + h * P + pbase + tid);
         if (tid == SSM_PC) ssm_cp4(dst + 2 * NP + SSM_PC, proj + (size_t)(row0 + i0 + r) * ld_p + dt_col0 + h);
@@ -116,6 +121,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
 
   load(0, 0);
   int s = 0;
+  float log_decay = 0.f;
   float* yo = y + (size_t)row0 * inner + h * P + p0 + (ns & 1);          // where lane ns < 2 stores column p0 + ns
   for (int i0 = 0; i0 < n_rows; i0 += ROWS, s ^= 1) {
     const int nr = min(ROWS, n_rows - i0);
@@ -131,12 +137,26 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
       t[1] = expf(a * dt);
     }
     __syncthreads();
+    if (STATE_ONLY && tid == 0 && blockIdx.y == 0)
+      for (int r = 0; r < nr; ++r) log_decay += a * stage[s][r][2 * NP + SSM_PC];
 #pragma unroll 4
     for (int r = 0; r < nr; ++r) {
       const float* row = stage[s][r];
       const float dt = row[2 * NP + SSM_PC], da = row[2 * NP + SSM_PC + 1];
       const float2 xv = *reinterpret_cast<const float2*>(row + 2 * NP + 2 * pl);
       const float2 u0 = make_float2(dt * xv.x, dt * xv.x), u1 = make_float2(dt * xv.y, dt * xv.y), dd = make_float2(da, da);
+      if (STATE_ONLY) {
+#pragma unroll
+        for (int k = 0; k < K4; ++k) {
+          const float4 b = *reinterpret_cast<const float4*>(row + 4 * (ns + SSM_NS * k));
+          const float2 blo = make_float2(b.x, b.y), bhi = make_float2(b.z, b.w);
+          S0[2 * k] = __ffma2_rn(S0[2 * k], dd, __fmul2_rn(blo, u0));
+          S1[2 * k] = __ffma2_rn(S1[2 * k], dd, __fmul2_rn(blo, u1));
+          S0[2 * k + 1] = __ffma2_rn(S0[2 * k + 1], dd, __fmul2_rn(bhi, u0));
+          S1[2 * k + 1] = __ffma2_rn(S1[2 * k + 1], dd, __fmul2_rn(bhi, u1));
+        }
+        continue;
+      }
       float2 a0 = make_float2(0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
       for (int k = 0; k < K4; ++k) {                          // two states per instruction (fma.rn.f32x2)
@@ -163,16 +183,80 @@ ssm_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   // dependent grid released at its start parks its blocks on every SM for all that time (measured on the 8-layer step:
   // 13.9 ms against 11.7 ms when every launch waits for the one before it).
   kf_pdl_trigger();
-  if (write_state) {
+  const int so = write_state ? slot_out[req] : -1;
+  if (so >= 0) {
+    float* dp0 = state_out + (((size_t)so * heads + h) * P + p0) * N;
 #pragma unroll
     for (int k = 0; k < K4; ++k)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int n = 4 * (ns + SSM_NS * k) + j;
         const float2 v0 = S0[2 * k + (j >> 1)], v1 = S1[2 * k + (j >> 1)];
-        if (p0 < P && n < N) sp0[n] = (j & 1) ? v0.y : v0.x;
-        if (p0 + 1 < P && n < N) sp0[N + n] = (j & 1) ? v1.y : v1.x;
+        if (p0 < P && n < N) dp0[n] = (j & 1) ? v0.y : v0.x;
+        if (p0 + 1 < P && n < N) dp0[N + n] = (j & 1) ? v1.y : v1.x;
       }
+    if (STATE_ONLY && tid == 0 && blockIdx.y == 0) decay_out[(size_t)so * heads + h] = expf(log_decay);
+  }
+}
+
+// ---- a long prompt in chunks that are walked side by side -------------------------------------------------------------
+// One request's state gives few blocks, and its rows depend on one another, so a lone long prompt leaves most of the GPU
+// waiting.  The recurrence is linear in the state, S_t = a_t S_(t-1) + u_t, so a prompt can be cut into chunks of L rows:
+//   1. every chunk but a request's last is walked from a ZERO state, which gives its own contribution E_k to the state at
+//      its end and the product D_k of its decays (the walk above in its STATE_ONLY form, all chunks side by side);
+//   2. the states at the chunks' starts follow one after the other, I_(k+1) = D_k I_k + E_k, from the request's stored
+//      state (an elementwise kernel, sequential over a request's chunks);
+//   3. every chunk is walked from its I_k exactly as an unchunked walk would pass through it, writing y, and a
+//      request's last chunk leaves the request's new state.
+// The arithmetic of step 3 is that of the plain walk; only the I_k are rounded differently (sums regrouped).
+
+__global__ void ssm_chunk_table_kernel(int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
+                                       const int* __restrict__ req_state_slot, int L, int max_chunks, int* __restrict__ tab) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int* c_row_start = tab;                                   // per chunk: first row, rows, rows if walked in step 1,
+  int* c_n_rows = tab + max_chunks;                         // its own index, the slot its end state goes to (or -1)
+  int* c_n_rows_a = tab + 2 * max_chunks;
+  int* c_ident = tab + 3 * max_chunks;
+  int* c_out_slot = tab + 4 * max_chunks;
+  int* r_chunk0 = tab + 5 * max_chunks;                     // per request: its first chunk and how many it has
+  int* r_nchunks = r_chunk0 + n_reqs;
+  int k = 0;
+  for (int r = 0; r < n_reqs; ++r) {
+    const int n = req_n_rows[r], nc = n > 0 ? (n + L - 1) / L : 0;
+    r_chunk0[r] = k;
+    r_nchunks[r] = nc;
+    for (int c = 0; c < nc && k < max_chunks; ++c, ++k) {
+      const int rows = min(L, n - c * L);
+      c_row_start[k] = req_row_start[r] + c * L;
+      c_n_rows[k] = rows;
+      c_n_rows_a[k] = c == nc - 1 ? 0 : rows;
+      c_ident[k] = k;
+      c_out_slot[k] = c == nc - 1 ? req_state_slot[r] : -1;
+    }
+  }
+  for (; k < max_chunks; ++k) { c_row_start[k] = 0; c_n_rows[k] = 0; c_n_rows_a[k] = 0; c_ident[k] = k; c_out_slot[k] = -1; }
+}
+
+__global__ void ssm_chunk_fold_kernel(const float* __restrict__ state, float* __restrict__ chunk_state,
+                                      const float* __restrict__ chunk_decay, int heads, int PN, int n_reqs,
+                                      const int* __restrict__ req_state_slot, const int* __restrict__ r_chunk0,
+                                      const int* __restrict__ r_nchunks) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int req = blockIdx.x, h = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  if (e >= PN) return;
+  const int nc = r_nchunks[req];
+  if (nc <= 0) return;
+  const int k0 = r_chunk0[req];
+  float S = state[((size_t)req_state_slot[req] * heads + h) * PN + e];
+  for (int c = 0; c < nc; ++c) {
+    float* at = chunk_state + ((size_t)(k0 + c) * heads + h) * PN + e;
+    const float own = c < nc - 1 ? *at : 0.f;               // E_k, left there by step 1
+    *at = S;                                                // I_k, read by step 3
+    if (c < nc - 1) S = fmaf(chunk_decay[(size_t)(k0 + c) * heads + h], S, own);
   }
 }
 
@@ -240,45 +324,104 @@ ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   }
 }
 
+// The staged walk is launched WITHOUT the programmatic-dependent-launch attribute: released early by its predecessor,
+// its blocks (37 KB of shared memory and a quarter of an SM's registers each) would sit on every SM waiting while the
+// kernels before it still need the room; measured on an 8-layer prompt step, 8.3 ms with the attribute, 6.5 ms without.
+template <typename TW, bool STATE_ONLY>
+static void ssm_launch_walk(dim3 grid, cudaStream_t stream, const float* xbc, int ld_x, const float* proj, int ld_p, int dt_col0,
+                            const void* dt_bias, const void* a_log, const void* d_skip, const float* state_in, const int* slot_in,
+                            float* state_out, const int* slot_out, float* decay_out, float* y, int heads, int groups, int P, int N,
+                            int n_reqs, const int* row_start, const int* n_rows, int write_state, int vec) {
+  const dim3 block(SSM_THREADS);
+#define KF_GO2(K4, ROWS)                                                                                                 \
+  ssm_scan_kernel<K4, ROWS, TW, STATE_ONLY><<<grid, block, 0, stream>>>(xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias, \
+      (const TW*)a_log, (const TW*)d_skip, state_in, slot_in, state_out, slot_out, decay_out, y, heads, groups, P, N, n_reqs, \
+      row_start, n_rows, write_state, vec)
+  if (N <= 32) KF_GO2(1, 16);
+  else if (N <= 64) KF_GO2(2, 16);
+  else if (N <= 128) KF_GO2(4, 16);
+  else KF_GO2(8, 8);
+#undef KF_GO2
+}
+
 KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, int dt_col0, const void* dt_bias,
                        const void* a_log, const void* d_skip, int w_dtype, float* state, float* y, int heads, int groups,
                        int P, int N, int n_reqs, const int* req_row_start, const int* req_n_rows,
                        const int* req_state_slot, int write_state, int single_rows, cudaStream_t stream) {
   if (n_reqs <= 0) return KF_OK;
   if (N < 1 || N > SSM_MAX_N || P < 1 || heads < 1 || groups < 1 || heads % groups) return KF_ERR_SIZE;
+  if (w_dtype != KF_F32 && w_dtype != KF_BF16) return KF_ERR_DTYPE;
   const dim3 grid(n_reqs * heads, kf_ceil_div(P, SSM_PC)), block(SSM_THREADS);
   // 16-byte copies when every offset into the rows is a multiple of four floats
   const int vec = (N % 4 == 0 && P % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
-// The staged walk is launched WITHOUT the programmatic-dependent-launch attribute: released early by its predecessor,
-// its blocks (37 KB of shared memory and a quarter of an SM's registers each) would sit on every SM waiting while the
-// kernels before it still need the room; measured on an 8-layer prompt step, 8.3 ms with the attribute, 6.5 ms without.
-#define KF_GO2(K4, ROWS, TW)                                                                                            \
-  ssm_scan_kernel<K4, ROWS, TW><<<grid, block, 0, stream>>>(xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,          \
-            (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
-            req_state_slot, write_state, vec)
+  if (single_rows) {
 #define KF_STEP(K4, TW)                                                                                                 \
   kf_launch(ssm_step_kernel<K4, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,         \
             (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
             req_state_slot, write_state)
-#define KF_GO(TW)                                      \
-  do {                                                 \
-    if (single_rows) {                                 \
-      if (N <= 32) KF_STEP(1, TW);                     \
-      else if (N <= 64) KF_STEP(2, TW);                \
-      else if (N <= 128) KF_STEP(4, TW);               \
-      else KF_STEP(8, TW);                             \
-    } else                                             \
-    if (N <= 32) KF_GO2(1, 16, TW);                    \
-    else if (N <= 64) KF_GO2(2, 16, TW);               \
-    else if (N <= 128) KF_GO2(4, 16, TW);              \
-    else KF_GO2(8, 8, TW);                             \
+#define KF_GO(TW)                                  \
+  do {                                             \
+    if (N <= 32) KF_STEP(1, TW);                   \
+    else if (N <= 64) KF_STEP(2, TW);              \
+    else if (N <= 128) KF_STEP(4, TW);             \
+    else KF_STEP(8, TW);                           \
   } while (0)
-  if (w_dtype == KF_F32) KF_GO(float);
-  else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);
-  else return KF_ERR_DTYPE;
+    if (w_dtype == KF_F32) KF_GO(float);
+    else KF_GO(__nv_bfloat16);
 #undef KF_GO
-#undef KF_GO2
 #undef KF_STEP
+  } else if (w_dtype == KF_F32) {
+    ssm_launch_walk<float, false>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, state, req_state_slot, state,
+                                  req_state_slot, nullptr, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows, write_state, vec);
+  } else {
+    ssm_launch_walk<__nv_bfloat16, false>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, state, req_state_slot,
+                                          state, req_state_slot, nullptr, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,
+                                          write_state, vec);
+  }
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// The same over chunks of `chunk_rows` rows walked side by side (see above).  Scratch from the caller: `tab`
+// (5 * max_chunks + 2 * n_reqs ints), `chunk_state` (max_chunks * heads * P * N floats) and `chunk_decay`
+// (max_chunks * heads floats), with max_chunks >= rows / chunk_rows + n_reqs.
+KF_API int kf_ssm_scan_chunked(const float* xbc, int ld_x, const float* proj, int ld_p, int dt_col0, const void* dt_bias,
+                               const void* a_log, const void* d_skip, int w_dtype, float* state, float* y, int heads,
+                               int groups, int P, int N, int n_reqs, const int* req_row_start, const int* req_n_rows,
+                               const int* req_state_slot, int write_state, int chunk_rows, int max_chunks, int* tab,
+                               float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+  if (n_reqs <= 0) return KF_OK;
+  if (N < 1 || N > SSM_MAX_N || P < 1 || heads < 1 || groups < 1 || heads % groups || chunk_rows < 1 || max_chunks < 1)
+    return KF_ERR_SIZE;
+  if (w_dtype != KF_F32 && w_dtype != KF_BF16) return KF_ERR_DTYPE;
+  const int vec = (N % 4 == 0 && P % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)xbc & 15) == 0) ? 1 : 0;
+  const int* c_row_start = tab;
+  const int* c_n_rows = tab + max_chunks;
+  const int* c_n_rows_a = tab + 2 * max_chunks;
+  const int* c_ident = tab + 3 * max_chunks;
+  const int* c_out_slot = tab + 4 * max_chunks;
+  const int* r_chunk0 = tab + 5 * max_chunks;
+  const int* r_nchunks = r_chunk0 + n_reqs;
+  kf_launch(ssm_chunk_table_kernel, dim3(1), dim3(32), 0, stream, n_reqs, req_row_start, req_n_rows, req_state_slot, chunk_rows,
+            max_chunks, tab);
+  const dim3 grid(max_chunks * heads, kf_ceil_div(P, SSM_PC));
+  if (w_dtype == KF_F32)
+    ssm_launch_walk<float, true>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, nullptr, c_ident, chunk_state,
+                                 c_ident, chunk_decay, nullptr, heads, groups, P, N, max_chunks, c_row_start, c_n_rows_a, 1, vec);
+  else
+    ssm_launch_walk<__nv_bfloat16, true>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, nullptr, c_ident,
+                                         chunk_state, c_ident, chunk_decay, nullptr, heads, groups, P, N, max_chunks, c_row_start,
+                                         c_n_rows_a, 1, vec);
+  const int PN = P * N;
+  kf_launch(ssm_chunk_fold_kernel, dim3(n_reqs, heads, kf_ceil_div(PN, 256)), dim3(256), 0, stream, (const float*)state, chunk_state,
+            (const float*)chunk_decay, heads, PN, n_reqs, req_state_slot, r_chunk0, r_nchunks);
+  if (w_dtype == KF_F32)
+    ssm_launch_walk<float, false>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, chunk_state, c_ident, state,
+                                  c_out_slot, nullptr, y, heads, groups, P, N, max_chunks, c_row_start, c_n_rows, write_state, vec);
+  else
+    ssm_launch_walk<__nv_bfloat16, false>(grid, stream, xbc, ld_x, proj, ld_p, dt_col0, dt_bias, a_log, d_skip, chunk_state, c_ident,
+                                          state, c_out_slot, nullptr, y, heads, groups, P, N, max_chunks, c_row_start, c_n_rows,
+                                          write_state, vec);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

@@ -251,6 +251,39 @@ def test_state_space_scan_in_portions(wdtype, heads, groups, P, N):
     assert float(state[1].min()) == 3.0 and float(y[-1].min()) == 5.0
 
 
+@pytest.mark.parametrize("heads,groups,P,N", [(2, 1, 16, 16), (3, 3, 12, 10), (4, 2, 64, 128)])
+def test_long_portions_walked_in_chunks_side_by_side(heads, groups, P, N, monkeypatch):
+    """Steps of many rows cut the recurrence into chunks (states at the chunks' starts from a first pass).
+    Requests of 700, 1 and 130 rows and one of 128 exactly (chunks of 128 here), two of them with a state from before; against the same
+    kernel walking every request in one piece, to rounding of the regrouped sums."""
+    from kungfu_b200 import ops
+    st = FakeStep(rows=(700, 1, 130, 128), before=(0, 5, 3, 0), slots=(2, 0, 3, 1))
+    g = torch.Generator().manual_seed(P + N)
+    inner = heads * P
+    ld_x, ld_p, dt0 = inner + 2 * groups * N, heads + 4, 2
+    a_log = (-4.0 + 2.0 * torch.rand(heads, generator=g)).to(DEV)
+    dt_bias, d_skip = (0.5 * torch.randn(heads, generator=g)).to(DEV), torch.randn(heads, generator=g).to(DEV)
+    xbc = torch.randn(st.n_rows, ld_x, generator=g).to(DEV)
+    proj = torch.randn(st.n_rows, ld_p, generator=g).to(DEV)
+    state0 = torch.randn(4, heads, P, N, generator=g).to(DEV)
+    state0[[2, 1]] = 0.0
+    out = {}
+    for chunked in (False, True):
+        monkeypatch.setattr(ops, "chunked_scan", chunked)
+        monkeypatch.setattr(ops, "SCAN_CHUNKED_FROM", 512)
+        monkeypatch.setattr(ops, "SCAN_CHUNK_ROWS", 128)
+        state = state0.clone()
+        y = torch.full((st.n_rows, inner), 7.0, device=DEV)
+        before = ops.launch_count()
+        ops.ssm_scan(xbc, proj, dt0, dt_bias, a_log, d_skip, state, y, heads, groups, P, N, st)
+        assert ops.launch_count() - before == (4 if chunked else 1)
+        out[chunked] = (y, state)
+    scale = float(out[False][0][:-1].abs().max())
+    assert float((out[True][0][:-1] - out[False][0][:-1]).abs().max()) / scale < 2e-5
+    assert float((out[True][1] - out[False][1]).abs().max()) / float(out[False][1].abs().max()) < 2e-5
+    assert float(out[True][0][-1].min()) == 7.0                              # the padding row
+
+
 @pytest.mark.parametrize("heads,groups,P,N,taps", [(2, 1, 16, 16, 3), (6, 3, 8, 40, 4), (4, 2, 64, 128, 4), (3, 1, 12, 10, 2)])
 def test_steps_of_single_rows_token_by_token(heads, groups, P, N, taps):
     """Decoding: every request brings one row, and the kernels then take other paths (the convolution moves its own
