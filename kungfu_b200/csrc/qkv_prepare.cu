@@ -19,6 +19,15 @@ __device__ __forceinline__ void kf_store_vec4(__nv_bfloat16* o, size_t i, float4
   *reinterpret_cast<uint2*>(o + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
 }
 
+// Four neighbouring elements p[i .. i+3] (i a multiple of four, the base 16-byte aligned) in one load.
+__device__ __forceinline__ float4 kf_load4(const float* p, size_t i) { return *reinterpret_cast<const float4*>(p + i); }
+__device__ __forceinline__ float4 kf_load4(const __nv_bfloat16* p, size_t i) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p + i);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 constexpr int QP_MAX_D = 256;
 constexpr int QP_WARPS = 4;
 
@@ -144,9 +153,14 @@ qkv_prepare_vec_kernel(KfConvIn cv, const TW* __restrict__ conv_w, const TW* __r
       x[r] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (i < d) {
         const int ch = chan0 + i;
-        float4 bi = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cv.in_bias) bi = make_float4(kf_load((const TW*)cv.in_bias, ch), kf_load((const TW*)cv.in_bias, ch + 1),
-                                         kf_load((const TW*)cv.in_bias, ch + 2), kf_load((const TW*)cv.in_bias, ch + 3));
+        const float4 bi = cv.in_bias ? kf_load4((const TW*)cv.in_bias, ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        // the filter taps of the lane's four channels: with four taps one load per channel
+        float4 w0, w1, w2, w3;                              // w_c = taps 0..3 of channel ch + c
+        const bool four = conv_w && cv.taps == 4;
+        if (four) {
+          w0 = kf_load4(conv_w, (size_t)ch * 4); w1 = kf_load4(conv_w, (size_t)ch * 4 + 4);
+          w2 = kf_load4(conv_w, (size_t)ch * 4 + 8); w3 = kf_load4(conv_w, (size_t)ch * 4 + 12);
+        }
         for (int j = 0; j < cv.taps; ++j) {
           const int idx = li - (cv.taps - 1 - j);
           float4 u;
@@ -156,7 +170,12 @@ qkv_prepare_vec_kernel(KfConvIn cv, const TW* __restrict__ conv_w, const TW* __r
           } else {
             u = *reinterpret_cast<const float4*>(cv.state + ((size_t)slot * (cv.taps - 1) + (cv.taps - 1 + idx)) * cv.C + ch);
           }
-          if (conv_w) {
+          if (four) {
+            const float t0 = j == 0 ? w0.x : j == 1 ? w0.y : j == 2 ? w0.z : w0.w, t1 = j == 0 ? w1.x : j == 1 ? w1.y : j == 2 ? w1.z : w1.w;
+            const float t2 = j == 0 ? w2.x : j == 1 ? w2.y : j == 2 ? w2.z : w2.w, t3 = j == 0 ? w3.x : j == 1 ? w3.y : j == 2 ? w3.z : w3.w;
+            x[r].x = fmaf(t0, u.x, x[r].x); x[r].y = fmaf(t1, u.y, x[r].y);
+            x[r].z = fmaf(t2, u.z, x[r].z); x[r].w = fmaf(t3, u.w, x[r].w);
+          } else if (conv_w) {
             x[r].x = fmaf(kf_load(conv_w, (size_t)ch * cv.taps + j), u.x, x[r].x);
             x[r].y = fmaf(kf_load(conv_w, (size_t)(ch + 1) * cv.taps + j), u.y, x[r].y);
             x[r].z = fmaf(kf_load(conv_w, (size_t)(ch + 2) * cv.taps + j), u.z, x[r].z);
@@ -179,8 +198,8 @@ qkv_prepare_vec_kernel(KfConvIn cv, const TW* __restrict__ conv_w, const TW* __r
       for (int r = 0; r < 2; ++r) {
         const int i = 4 * lane + 128 * r;
         if (i < d) {
-          x[r].x *= inv * kf_load(nw, i); x[r].y *= inv * kf_load(nw, i + 1);
-          x[r].z *= inv * kf_load(nw, i + 2); x[r].w *= inv * kf_load(nw, i + 3);
+          const float4 g = kf_load4(nw, i);
+          x[r].x *= inv * g.x; x[r].y *= inv * g.y; x[r].z *= inv * g.z; x[r].w *= inv * g.w;
         }
       }
     }
@@ -216,6 +235,7 @@ KF_API int kf_qkv_prepare(const float* in, int ld, int col0, const void* in_bias
   KfConvIn cv{in, ld, col0, in_bias, conv_state, nh * dk + nkv * dk + nkv * dv, taps};
   const bool vec = dk % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && rot % 4 == 0 && (interleaved || rot == 0) && ld % 4 == 0 &&
                    col0 % 4 == 0 && (((uintptr_t)in | (uintptr_t)conv_state | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0 &&
+                   (((uintptr_t)in_bias | (uintptr_t)conv_w | (uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0 &&
                    (((uintptr_t)cos_t | (uintptr_t)sin_t) & 7) == 0;
   const bool commit = commit_inline && conv_w && taps > 1;
   if (commit && !vec) return KF_ERR_ALIGN;                  // the caller asks `kf_qkv_prepare_commits_inline` first
