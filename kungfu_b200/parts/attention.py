@@ -16,7 +16,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import FixedState, Mixer, PagedKV, PositionEncoding, StateBundle, pad_rows, register_mixer
+from .base import Mixer, PagedKV, PositionEncoding, StateBundle, pad_rows, register_mixer
 from .conv import ShortConv
 
 
