@@ -269,7 +269,7 @@ ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
                 const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
                 float* __restrict__ state, float* __restrict__ y, int heads, int groups, int P, int N,
                 int n_reqs, const int* __restrict__ req_row_start, const int* __restrict__ req_n_rows,
-                const int* __restrict__ req_state_slot, int write_state) {
+                const int* __restrict__ req_state_slot, int write_state, int vec) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const int req = blockIdx.x / heads, h = blockIdx.x - req * heads;
@@ -282,6 +282,22 @@ ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
   const float* row = xbc + (size_t)t * ld_x;
   float* sp0 = state + (((size_t)slot * heads + h) * P + p0) * N;
   float2 S0[2 * K4], S1[2 * K4], bb[2 * K4], cc[2 * K4];
+  if (vec) {                                                // groups of four states in 16-byte loads (N a multiple of four)
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < K4; ++k) {
+      const int n = 4 * (ns + SSM_NS * k);
+      const bool in = n < N;
+      const float4 v0 = (in && p0 < P) ? *reinterpret_cast<const float4*>(sp0 + n) : zero4;
+      const float4 v1 = (in && p0 + 1 < P) ? *reinterpret_cast<const float4*>(sp0 + N + n) : zero4;
+      const float4 b = in ? *reinterpret_cast<const float4*>(row + inner + g * N + n) : zero4;
+      const float4 c = in ? *reinterpret_cast<const float4*>(row + inner + (groups + g) * N + n) : zero4;
+      S0[2 * k] = make_float2(v0.x, v0.y); S0[2 * k + 1] = make_float2(v0.z, v0.w);
+      S1[2 * k] = make_float2(v1.x, v1.y); S1[2 * k + 1] = make_float2(v1.z, v1.w);
+      bb[2 * k] = make_float2(b.x, b.y); bb[2 * k + 1] = make_float2(b.z, b.w);
+      cc[2 * k] = make_float2(c.x, c.y); cc[2 * k + 1] = make_float2(c.z, c.w);
+    }
+  } else
 #pragma unroll
   for (int k = 0; k < K4; ++k)
 #pragma unroll
@@ -311,7 +327,15 @@ ssm_step_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
 #pragma unroll
   for (int o = 2; o < SSM_NS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   if (ns < 2 && p0 + ns < P) y[(size_t)t * inner + h * P + p0 + ns] = fmaf(kf_load(d_skip, h), ns ? x1 : x0, v);
-  if (write_state) {
+  if (write_state && vec) {
+#pragma unroll
+    for (int k = 0; k < K4; ++k) {
+      const int n = 4 * (ns + SSM_NS * k);
+      if (n >= N) continue;
+      if (p0 < P) *reinterpret_cast<float4*>(sp0 + n) = make_float4(S0[2 * k].x, S0[2 * k].y, S0[2 * k + 1].x, S0[2 * k + 1].y);
+      if (p0 + 1 < P) *reinterpret_cast<float4*>(sp0 + N + n) = make_float4(S1[2 * k].x, S1[2 * k].y, S1[2 * k + 1].x, S1[2 * k + 1].y);
+    }
+  } else if (write_state) {
 #pragma unroll
     for (int k = 0; k < K4; ++k)
 #pragma unroll
@@ -358,7 +382,7 @@ KF_API int kf_ssm_scan(const float* xbc, int ld_x, const float* proj, int ld_p, 
 #define KF_STEP(K4, TW)                                                                                                 \
   kf_launch(ssm_step_kernel<K4, TW>, grid, block, 0, stream, xbc, ld_x, proj, ld_p, dt_col0, (const TW*)dt_bias,         \
             (const TW*)a_log, (const TW*)d_skip, state, y, heads, groups, P, N, n_reqs, req_row_start, req_n_rows,      \
-            req_state_slot, write_state)
+            req_state_slot, write_state, (vec && (((uintptr_t)state) & 15) == 0) ? 1 : 0)
 #define KF_GO(TW)                                  \
   do {                                             \
     if (N <= 32) KF_STEP(1, TW);                   \
