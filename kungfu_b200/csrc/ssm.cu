@@ -452,7 +452,7 @@ KF_API int kf_ssm_scan_chunked(const float* xbc, int ld_x, const float* proj, in
 
 // out[t][j] = rms_part(y[t] * silu(z[t]))[j] * w[j]: the gate is applied first, then every one of `parts` equal parts
 // of the row is divided by its own root mean square (eps inside the root).  z is columns z_col0.. of a 32-bit matrix
-// with ld columns.  One block per (row, part); sums in 32-bit.
+// with ld columns.  One block per (row, part); sums in 32-bit; y and z are read once (a thread keeps its gated values).
 template <typename TW, typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ld, int z_col0,
                                         const TW* __restrict__ w, float eps, int inner, int parts, TO* __restrict__ out,
@@ -460,6 +460,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
   kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ float red[33];
+  constexpr int KEEP = 8;                                   // gated values a thread keeps between the two passes
   const int t = blockIdx.x, part = blockIdx.y;
   const int len = inner / parts, j0 = part * len;
   if (row_req[t] < 0) {
@@ -468,18 +469,34 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
   }
   const float* yr = y + (size_t)t * inner + j0;
   const float* zr = z + (size_t)t * ld + z_col0 + j0;
+  float v[KEEP];
   float ss = 0.f;
-  for (int j = threadIdx.x; j < len; j += blockDim.x) {
+#pragma unroll
+  for (int c = 0; c < KEEP; ++c) {
+    const int j = threadIdx.x + c * blockDim.x;
+    v[c] = 0.f;
+    if (j < len) {
+      const float zz = zr[j];
+      v[c] = yr[j] * (zz / (1.f + expf(-zz)));
+      ss = fmaf(v[c], v[c], ss);
+    }
+  }
+  for (int j = threadIdx.x + KEEP * blockDim.x; j < len; j += blockDim.x) {       // parts longer than KEEP per thread
     const float zz = zr[j];
-    const float v = yr[j] * (zz / (1.f + expf(-zz)));
-    ss = fmaf(v, v, ss);
+    const float u = yr[j] * (zz / (1.f + expf(-zz)));
+    ss = fmaf(u, u, ss);
   }
   ss = kf_block_sum(ss, red);
   const float inv = 1.f / sqrtf(ss / (float)len + eps);
-  for (int j = threadIdx.x; j < len; j += blockDim.x) {
+#pragma unroll
+  for (int c = 0; c < KEEP; ++c) {
+    const int j = threadIdx.x + c * blockDim.x;
+    if (j < len) kf_store(out, (size_t)t * inner + j0 + j, v[c] * inv * kf_load(w, j0 + j));
+  }
+  for (int j = threadIdx.x + KEEP * blockDim.x; j < len; j += blockDim.x) {
     const float zz = zr[j];
-    const float v = yr[j] * (zz / (1.f + expf(-zz)));
-    kf_store(out, (size_t)t * inner + j0 + j, v * inv * kf_load(w, j0 + j));
+    const float u = yr[j] * (zz / (1.f + expf(-zz)));
+    kf_store(out, (size_t)t * inner + j0 + j, u * inv * kf_load(w, j0 + j));
   }
 }
 
@@ -489,7 +506,8 @@ KF_API int kf_gated_group_norm(const float* y, const float* z, int ld, int z_col
   if (T <= 0) return KF_OK;
   if (parts < 1 || inner % parts) return KF_ERR_SIZE;
   const int len = inner / parts;
-  const int threads = len >= 1024 ? 256 : 128;
+  // few rows (decoding): as many threads as the part has groups of four; many rows: blocks of at most 512 threads
+  const int threads = (len >= 4096 && T < 256) ? 1024 : (len >= 2048 ? 512 : (len >= 1024 ? 256 : 128));
   const dim3 grid(T, parts);
 #define KF_GO(TW, TO)                                                                                                \
   kf_launch(gated_group_norm_kernel<TW, TO>, grid, dim3(threads), 0, stream, y, z, ld, z_col0, (const TW*)w, eps, inner, \
