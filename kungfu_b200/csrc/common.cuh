@@ -100,7 +100,7 @@ __device__ __forceinline__ float kf_block_sum(float v, float* red) {
 }
 
 // activations of the gated feed-forward
-enum KfAct { KF_ACT_GELU_TANH = 0, KF_ACT_GELU_ERF = 1, KF_ACT_SILU = 2 };
+enum KfAct { KF_ACT_GELU_TANH = 0, KF_ACT_GELU_ERF = 1, KF_ACT_SILU = 2, KF_ACT_CLAMPED_SWISH = 3 };   // 3: gated form only
 
 __device__ __forceinline__ float kf_act(float x, int act) {
   if (act == KF_ACT_GELU_TANH) {
@@ -110,6 +110,13 @@ __device__ __forceinline__ float kf_act(float x, int act) {
     return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
   }
   return x / (1.f + expf(-x));
+}
+
+// The clamped gated form: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float kf_clamped_swish(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
 }
 
 __device__ __forceinline__ float kf_softcap(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }

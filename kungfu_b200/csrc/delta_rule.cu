@@ -1,0 +1,232 @@
+// The gated delta rule: a recurrent mixer whose state per head is a d x dv matrix S of 32-bit floats (rows = key
+// channels, columns = value channels) that is decayed, corrected towards the current value and read, token by token:
+//   S <- diag(g_t) S          g_t: one decay per head, or one per head and key channel (rows of S)
+//   u  = beta_t (v_t - S^T k_t)
+//   S <- S + k_t u^T
+//   o_t = S^T q_t             (the read-out sees the current token's write)
+// with q, k unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^(-1/2), beta = sigmoid(raw),
+// g = exp(-exp(A_log_h) * softplus(raw + dt_bias)).  Query/key head of value head h: h / (heads / kv_heads).
+// Everything here is 32-bit.  The tokens of a request are walked in order with the same arithmetic whatever the step
+// holds of it (one token, a portion, a whole prompt): a token's result depends on the cut only through nothing at all,
+// since the state is carried exactly.
+//
+// Work split: a block of 128 threads owns (request, head, 32 value columns).  Thread (c, l) keeps rows
+// l*NR .. l*NR+NR-1 of column c in registers (d <= 4 NR; rows beyond d are zero and stay zero); the four lanes of a
+// column add their partial dot products by two shuffles.  Rows of q, k, the decays, v and beta of R tokens at a time
+// are staged in shared memory, where the unit norms, the sigmoid and the decays (the transcendental work) are done by
+// all threads side by side, so that the serial walk is multiply-adds and shared loads only.  A lane's chunk of a staged
+// row starts every NR + 4 floats: the four lanes of a column then read four different banks with 16-byte loads.
+//
+// kf_head_norm_gate follows: every head's o is divided by its root mean square over dv, times a weight vector shared
+// by the heads, times silu or sigmoid of a gate column.
+#include "common.cuh"
+
+struct KfDeltaArgs {
+  const float* qkv; int ld_qkv, q0, k0, v0;      // 32-bit rows after the short convolution and its activation
+  const float* beta; int ld_beta, beta0;         // raw beta of head h: column beta0 + h
+  const float* decay; int ld_decay, decay0;      // raw decay: column decay0 + h, or decay0 + h * d + i per key channel
+  int per_channel;
+  const void* dt_bias; const void* a_log;        // [H] or [H * d]; [H]
+  float* state;                                  // [slots, H, d, dv]
+  float* out; int ld_out;                        // [rows, H * dv]
+  int H, KH, d, dv, n_reqs;
+  const int* req_row_start; const int* req_n_rows; const int* req_state_slot;
+  int writes;
+};
+
+__device__ __forceinline__ float kf_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+template <typename TW, int NR>
+__global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  constexpr int R = NR >= 64 ? 8 : 16;
+  constexpr int LS = NR + 4;
+  constexpr int ROW = 4 * LS;
+  __shared__ __align__(16) float q_s[R][ROW];
+  __shared__ __align__(16) float k_s[R][ROW];
+  __shared__ __align__(16) float g_s[R][ROW];
+  __shared__ float v_s[R][32];
+  __shared__ float beta_s[R], g1_s[R];
+  const int req = blockIdx.x / p.H, h = blockIdx.x - req * p.H;
+  const int n = p.req_n_rows[req];
+  if (n <= 0) return;
+  const int row0 = p.req_row_start[req], slot = p.req_state_slot[req];
+  const int kh = h / (p.H / p.KH);
+  const int tid = threadIdx.x, c = tid >> 2, l = tid & 3, lane = tid & 31, warp = tid >> 5;
+  const int col0 = blockIdx.y * 32, col = col0 + c;
+  const bool col_ok = col < p.dv;
+  const int d = p.d, dv = p.dv;
+  float S[NR];
+  float* sp = p.state + ((size_t)slot * p.H + h) * d * dv;
+#pragma unroll
+  for (int i = 0; i < NR; ++i) {
+    const int r = l * NR + i;
+    S[i] = (r < d && col_ok) ? sp[(size_t)r * dv + col] : 0.f;
+  }
+  const float rate = expf(kf_load((const TW*)p.a_log, h));
+  const float q_scale = 1.f / sqrtf((float)d);
+
+  for (int t0 = 0; t0 < n; t0 += R) {
+    const int nr = min(R, n - t0);
+    __syncthreads();                             // the walk over the rows staged before is over
+    for (int idx = tid; idx < nr * 4 * NR; idx += 128) {
+      const int tt = idx / (4 * NR), i = idx - tt * 4 * NR;
+      const int at = (i / NR) * LS + (i % NR);
+      const size_t row = (size_t)(row0 + t0 + tt);
+      const bool in = i < d;
+      q_s[tt][at] = in ? p.qkv[row * p.ld_qkv + p.q0 + kh * d + i] : 0.f;
+      k_s[tt][at] = in ? p.qkv[row * p.ld_qkv + p.k0 + kh * d + i] : 0.f;
+      if (p.per_channel) {
+        float g = 1.f;
+        if (in) {
+          const float raw = p.decay[row * p.ld_decay + p.decay0 + h * d + i] + kf_load((const TW*)p.dt_bias, h * d + i);
+          g = expf(-rate * kf_softplus(raw));
+        }
+        g_s[tt][at] = g;
+      }
+    }
+    for (int idx = tid; idx < nr * 32; idx += 128) {
+      const int tt = idx >> 5, cc = idx & 31;
+      v_s[tt][cc] = (col0 + cc < dv) ? p.qkv[(size_t)(row0 + t0 + tt) * p.ld_qkv + p.v0 + h * dv + col0 + cc] : 0.f;
+    }
+    if (tid < nr) {
+      const size_t row = (size_t)(row0 + t0 + tid);
+      beta_s[tid] = 1.f / (1.f + expf(-p.beta[row * p.ld_beta + p.beta0 + h]));
+      if (!p.per_channel) {
+        const float raw = p.decay[row * p.ld_decay + p.decay0 + h] + kf_load((const TW*)p.dt_bias, h);
+        g1_s[tid] = expf(-rate * kf_softplus(raw));
+      }
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nr; tt += 4) {        // unit vectors: one warp per staged token
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < 4 * NR; i += 32) {
+        const int at = (i / NR) * LS + (i % NR);
+        sq = fmaf(q_s[tt][at], q_s[tt][at], sq);
+        sk = fmaf(k_s[tt][at], k_s[tt][at], sk);
+      }
+      sq = kf_warp_sum(sq);
+      sk = kf_warp_sum(sk);
+      const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
+      for (int i = lane; i < 4 * NR; i += 32) {
+        const int at = (i / NR) * LS + (i % NR);
+        q_s[tt][at] *= fq;
+        k_s[tt][at] *= fk;
+      }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nr; ++tt) {              // the walk
+      const float* kq = &k_s[tt][l * LS];
+      const float* qq = &q_s[tt][l * LS];
+      float kv = 0.f;
+      if (p.per_channel) {
+        const float* gq = &g_s[tt][l * LS];
+#pragma unroll
+        for (int i = 0; i < NR; i += 4) {
+          const float4 g4 = *reinterpret_cast<const float4*>(gq + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
+          kv = fmaf(S[i], k4.x, kv); kv = fmaf(S[i + 1], k4.y, kv); kv = fmaf(S[i + 2], k4.z, kv); kv = fmaf(S[i + 3], k4.w, kv);
+        }
+      } else {
+        const float g = g1_s[tt];
+#pragma unroll
+        for (int i = 0; i < NR; i += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
+          kv = fmaf(S[i], k4.x, kv); kv = fmaf(S[i + 1], k4.y, kv); kv = fmaf(S[i + 2], k4.z, kv); kv = fmaf(S[i + 3], k4.w, kv);
+        }
+      }
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float u = beta_s[tt] * (v_s[tt][c] - kv);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
+        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
+        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
+        o = fmaf(S[i], q4.x, o); o = fmaf(S[i + 1], q4.y, o); o = fmaf(S[i + 2], q4.z, o); o = fmaf(S[i + 3], q4.w, o);
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (l == 0 && col_ok) p.out[(size_t)(row0 + t0 + tt) * p.ld_out + h * dv + col] = o;
+    }
+  }
+  if (p.writes) {
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+      const int r = l * NR + i;
+      if (r < d && col_ok) sp[(size_t)r * dv + col] = S[i];
+    }
+  }
+}
+
+// d up to 256 key channels, any dv.  Rows of single-token steps and of prompt portions run the same kernel.
+KF_API int kf_delta_rule(const float* qkv, int ld_qkv, int q0, int k0, int v0, const float* beta, int ld_beta, int beta0,
+                         const float* decay, int ld_decay, int decay0, int per_channel, const void* dt_bias, const void* a_log,
+                         int w_dtype, float* state, float* out, int ld_out, int H, int KH, int d, int dv, int n_reqs,
+                         const int* req_row_start, const int* req_n_rows, const int* req_state_slot, int writes,
+                         cudaStream_t stream) {
+  if (n_reqs <= 0) return KF_OK;
+  if (d < 1 || d > 256 || dv < 1 || H < 1 || KH < 1 || H % KH) return KF_ERR_SIZE;
+  KfDeltaArgs p{qkv, ld_qkv, q0, k0, v0, beta, ld_beta, beta0, decay, ld_decay, decay0, per_channel, dt_bias, a_log,
+                state, out, ld_out, H, KH, d, dv, n_reqs, req_row_start, req_n_rows, req_state_slot, writes};
+  const dim3 grid(n_reqs * H, kf_ceil_div(dv, 32));
+#define KF_GO(TW)                                                                                            \
+  do {                                                                                                       \
+    if (d <= 32) kf_launch(delta_rule_kernel<TW, 8>, grid, dim3(128), 0, stream, p);                        \
+    else if (d <= 64) kf_launch(delta_rule_kernel<TW, 16>, grid, dim3(128), 0, stream, p);                  \
+    else if (d <= 128) kf_launch(delta_rule_kernel<TW, 32>, grid, dim3(128), 0, stream, p);                 \
+    else kf_launch(delta_rule_kernel<TW, 64>, grid, dim3(128), 0, stream, p);                               \
+  } while (0)
+  if (w_dtype == KF_F32) KF_GO(float);
+  else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+// out[t, h*dv + i] = o[t, h*dv + i] / sqrt(mean_i(o[t, h, :]^2) + eps) * w[i] * act(gate[t, gate0 + h*dv + i]),
+// act: 0 = silu, 1 = sigmoid.  One warp per (row, head).
+template <typename TW, typename TO>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const TW* __restrict__ w, float eps,
+                                      const float* __restrict__ gate, int ld_gate, int gate0, int act,
+                                      TO* __restrict__ out, int H, int dv, int T) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item - (long)t * H);
+  const float* src = o + ((size_t)t * H + h) * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss = fmaf(src[i], src[i], ss);
+  ss = kf_warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)dv + eps);
+  const float* g = gate + (size_t)t * ld_gate + gate0 + h * dv;
+  for (int i = lane; i < dv; i += 32) {
+    const float z = g[i];
+    const float s = 1.f / (1.f + expf(-z));
+    kf_store(out, ((size_t)t * H + h) * dv + i, src[i] * inv * kf_load(w, i) * (act == 0 ? z * s : s));
+  }
+}
+
+KF_API int kf_head_norm_gate(const float* o, const void* w, int w_dtype, float eps, const float* gate, int ld_gate, int gate0,
+                             int act, void* out, int out_dtype, int H, int dv, int T, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  const dim3 grid(kf_ceil_div((long)T * H, 4));
+#define KF_GO(TW, TO) \
+  kf_launch(head_norm_gate_kernel<TW, TO>, grid, dim3(128), 0, stream, o, (const TW*)w, eps, gate, ld_gate, gate0, act, (TO*)out, H, dv, T)
+  if (w_dtype == KF_F32 && out_dtype == KF_F32) KF_GO(float, float);
+  else if (w_dtype == KF_BF16 && out_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == KF_BF16 && out_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
+  else if (w_dtype == KF_F32 && out_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

@@ -67,27 +67,29 @@ KF_API int kf_rope_table(const int* positions, const float* inv_freq, float* cos
 // out[t, j] = act(gu[t, j]) * gu[t, I + j]: gate columns first, up columns second.
 // Reference: crates/kf-backend-cuda/src/kernels/elementwise.cu:42-44.
 template <typename TI, typename TO>
-__global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int I, int act) {
+__global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int I, int act, float limit) {
   kf_pdl_trigger();
   kf_pdl_wait();
   const size_t n = (size_t)T * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I, j = idx - t * I;
     const float g = kf_load(gu, t * 2 * I + j), u = kf_load(gu, t * 2 * I + I + j);
-    kf_store(out, idx, kf_act(g, act) * u);
+    kf_store(out, idx, act == KF_ACT_CLAMPED_SWISH ? kf_clamped_swish(g, u, limit) : kf_act(g, act) * u);
   }
 }
 
-KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int act, cudaStream_t stream) {
+// act 3 (the clamped form, see kf_clamped_swish) reads `limit`.
+KF_API int kf_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int act, float limit,
+                        cudaStream_t stream) {
   if (T <= 0) return KF_OK;
   const size_t n = (size_t)T * I;
   const int blocks = (int)((n + 255) / 256 > kf_sm_count() * 16 ? kf_sm_count() * 16 : (n + 255) / 256);
   if (in_dtype == KF_F32 && out_dtype == KF_F32)
-    kf_launch(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, T, I, act);
+    kf_launch(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, T, I, act, limit);
   else if (in_dtype == KF_F32 && out_dtype == KF_BF16)
-    kf_launch(gated_act_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (__nv_bfloat16*)out, T, I, act);
+    kf_launch(gated_act_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (__nv_bfloat16*)out, T, I, act, limit);
   else if (in_dtype == KF_BF16 && out_dtype == KF_BF16)
-    kf_launch(gated_act_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, act);
+    kf_launch(gated_act_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, act, limit);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();

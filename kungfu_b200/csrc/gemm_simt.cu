@@ -12,7 +12,7 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                 int T, int N, int K, float softcap) {
+                 int T, int N, int K, float softcap, long ldx) {
   kf_pdl_trigger();
   kf_pdl_wait();
   __shared__ float xs[BK][BM + 4];
@@ -30,7 +30,7 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
   for (int k0 = 0; k0 < K; k0 += BK) {
     {
       const int r = row0 + lr;
-      const TX* p = x + (size_t)r * K + k0 + lk;
+      const TX* p = x + (size_t)r * ldx + k0 + lk;
 #pragma unroll
       for (int u = 0; u < 4; ++u) xs[lk + u][lr] = (r < T && k0 + lk + u < K) ? kf_load(p, u) : 0.f;
       const int c = col0 + lr;
@@ -66,12 +66,14 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
 }
 
 template <typename TX, typename TW>
-static int launch(const TX* x, const TW* w, void* out, int out_dtype, int T, int N, int K, float softcap, cudaStream_t s) {
+static int launch(const TX* x, const TW* w, void* out, int out_dtype, int T, int N, int K, float softcap, cudaStream_t s,
+                  long ldx = 0) {
+  if (ldx <= 0) ldx = K;
   dim3 grid(kf_ceil_div(N, BN), kf_ceil_div(T, BM));
   if (out_dtype == KF_F32)
-    kf_launch(gemm_simt_kernel<TX, TW, float>, dim3(grid), dim3(256), 0, s, x, w, (float*)out, T, N, K, softcap);
+    kf_launch(gemm_simt_kernel<TX, TW, float>, dim3(grid), dim3(256), 0, s, x, w, (float*)out, T, N, K, softcap, ldx);
   else if (out_dtype == KF_BF16)
-    kf_launch(gemm_simt_kernel<TX, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, x, w, (__nv_bfloat16*)out, T, N, K, softcap);
+    kf_launch(gemm_simt_kernel<TX, TW, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, x, w, (__nv_bfloat16*)out, T, N, K, softcap, ldx);
   else
     return KF_ERR_DTYPE;
   KF_CHECK_LAUNCH();
@@ -87,5 +89,16 @@ KF_API int kf_linear_simt(const void* x, int x_dtype, const void* w, int w_dtype
   if (x_dtype == KF_BF16 && w_dtype == KF_BF16) return launch((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, out_dtype, T, N, K, softcap, stream);
   if (x_dtype == KF_F32 && w_dtype == KF_BF16) return launch((const float*)x, (const __nv_bfloat16*)w, out, out_dtype, T, N, K, softcap, stream);
   if (x_dtype == KF_BF16 && w_dtype == KF_F32) return launch((const __nv_bfloat16*)x, (const float*)w, out, out_dtype, T, N, K, softcap, stream);
+  return KF_ERR_DTYPE;
+}
+
+// The same product over a column range of a wider 32-bit matrix: x[t, k] = base[t * ldx + col0 + k].  The low-rank
+// second halves of factored projections read their inputs this way, straight from the stacked projection's result.
+KF_API int kf_linear_simt_cols(const float* base, long ldx, long col0, const void* w, int w_dtype, void* out, int out_dtype,
+                               int T, int N, int K, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return KF_OK;
+  if (K <= 0 || ldx < col0 + K) return KF_ERR_SIZE;
+  if (w_dtype == KF_F32) return launch(base + col0, (const float*)w, out, out_dtype, T, N, K, 0.f, stream, ldx);
+  if (w_dtype == KF_BF16) return launch(base + col0, (const __nv_bfloat16*)w, out, out_dtype, T, N, K, 0.f, stream, ldx);
   return KF_ERR_DTYPE;
 }

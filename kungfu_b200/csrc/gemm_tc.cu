@@ -166,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int pw = GATED ? 2 * up_offset : N;                                  // width of a partial row
 
     auto finish = [&](float v, float u) -> float {
-      if (EPI == EPI_GATED) return act_fast(v, act) * u;
+      if (EPI == EPI_GATED) return gated_fast(v, u, act, softcap);
       if (EPI == EPI_F32) return kf_softcap(v, softcap);
       return act > 0 ? act_fast(v, act - 1) : v;                               // bfloat16 store: act - 1 names an activation
     };
@@ -440,7 +440,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
           const int t = t0 + c0 + j;
           if (t < T && f < n_feat) {
             float r;
-            if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
+            if (EPI == EPI_GATED) r = gated_fast(v[j], u[j], act, softcap);
             else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
             else r = act > 0 ? act_fast(v[j], act - 1) : v[j];
             if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
@@ -742,7 +742,7 @@ gemm_tc_pair_body(const CUtensorMap& tm_w, const CUtensorMap& tm_x, void* __rest
             const int t = t0 + c0 + j;
             if (t < T && f < n_feat) {
               float r;
-              if (EPI == EPI_GATED) r = act_fast(v[j], act) * u[j];
+              if (EPI == EPI_GATED) r = gated_fast(v[j], u[j], act, softcap);
               else if (EPI == EPI_F32) r = kf_softcap(v[j], softcap);
               else r = act > 0 ? act_fast(v[j], act - 1) : v[j];
               if (EPI == EPI_F32) ((float*)out)[(size_t)t * ld_out + f] = r;
@@ -1499,7 +1499,7 @@ KF_API int kf_linear_tc_plan(int T, int N_features, int K, int gated, int* bn_ou
 
 // mode: 0 = 32-bit out (softcap > 0 applies the cap), 1 = bfloat16 out (act > 0: activation act - 1 on the way out, the
 // first half of a feed-forward without a gate), 2 = gated: w = [gate; up] stacked
-// ([2*N, K]), out[T, N] = act(gate) * up in bfloat16.  `partial` must hold splits * T * (gated ? 2N : N) floats when
+// ([2*N, K]), out[T, N] = act(gate) * up in bfloat16 (act 3: the clamped form of `gated_fast`, `softcap` holding its limit).  `partial` must hold splits * T * (gated ? 2N : N) floats when
 // the plan says splits > 1; `counters` one zero-initialised int per output tile (they are left zero).
 KF_API int kf_linear_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, float softcap, int act,
                         int bn, int splits, float* partial, int* counters, int* error_flag, cudaStream_t stream) {

@@ -1,0 +1,127 @@
+// Small row kernels of blocks with layer scales, a per-token side input and a latent key/value cache.
+//
+// kf_latent_append:      c = rms_norm(proj[t, c0 .. c0 + rank)) * w, written into the request's page at the token's
+//                        position, once as the key row and once as the value row of a single key/value head of D >= rank
+//                        elements (tails zero): attention in the latent space reads the same row as key and as value.
+// kf_scale_add_rmsnorm:  x[t] += a[t] * s (s: one factor per column), 32-bit; optionally next = rms_norm(x[t]) * g in the
+//                        same pass, and optionally a plain copy of the new x[t] in another element type.
+// kf_side_gate:          out[t, j] = gelu_tanh(gate[t, j]) * table[token[t], col0 + j]: the gate of a per-token input whose
+//                        second factor is looked up by token id.
+#include "common.cuh"
+
+template <typename TW, typename TC>
+__global__ void latent_append_kernel(const float* __restrict__ proj, int ld, int c0, int rank, const TW* __restrict__ w, float eps,
+                                     const int* __restrict__ positions, const int* __restrict__ row_req,
+                                     const int* __restrict__ table, int table_width, int page_size, TC* __restrict__ pages, int D) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int req = row_req[t];
+  if (req < 0) return;
+  const float* src = proj + (size_t)t * ld + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+  ss = kf_block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)rank + eps);
+  const int pos = positions[t];
+  const int page = table[(size_t)req * table_width + pos / page_size];
+  if (page < 0) return;
+  TC* kdst = pages + (((size_t)page * 2 + 0) * page_size + pos % page_size) * D;
+  TC* vdst = pages + (((size_t)page * 2 + 1) * page_size + pos % page_size) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = i < rank ? src[i] * inv * kf_load(w, i) : 0.f;
+    kf_store(kdst, i, v);
+    kf_store(vdst, i, v);
+  }
+}
+
+KF_API int kf_latent_append(const float* proj, int ld, int c0, int rank, const void* w, int w_dtype, float eps,
+                            const int* positions, const int* row_req, const int* table, int table_width, int page_size,
+                            void* pages, int pages_dtype, int D, int T, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  if (rank < 1 || rank > D) return KF_ERR_SIZE;
+#define KF_GO(TW, TC)                                                                                                        \
+  kf_launch(latent_append_kernel<TW, TC>, dim3(T), dim3(128), 0, stream, proj, ld, c0, rank, (const TW*)w, eps, positions, \
+            row_req, table, table_width, page_size, (TC*)pages, D)
+  if (w_dtype == KF_F32 && pages_dtype == KF_F32) KF_GO(float, float);
+  else if (w_dtype == KF_BF16 && pages_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == KF_BF16 && pages_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
+  else if (w_dtype == KF_F32 && pages_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+template <typename TS, typename TW, typename TO, typename TC>
+__global__ void scale_add_rmsnorm_kernel(const float* __restrict__ a, const TS* __restrict__ s, float* __restrict__ x,
+                                         const TW* __restrict__ w, float eps, int plus_one, TO* __restrict__ out,
+                                         TC* __restrict__ copy, int H) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = fmaf(a[base + i], kf_load(s, i), x[base + i]);
+    x[base + i] = v;
+    if (copy) kf_store(copy, base + i, v);
+    ss = fmaf(v, v, ss);
+  }
+  if (!out) return;
+  ss = kf_block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float g = kf_load(w, i) + (plus_one ? 1.f : 0.f);
+    kf_store(out, base + i, x[base + i] * inv * g);
+  }
+}
+
+// s, w share one element type (the model's); out and copy share one (the step's activation type).
+KF_API int kf_scale_add_rmsnorm(const float* a, const void* s, int s_dtype, float* x, const void* w, float eps, int plus_one,
+                                void* out, void* copy, int out_dtype, int T, int H, cudaStream_t stream) {
+  if (T <= 0) return KF_OK;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define KF_GO(TS, TO)                                                                                                     \
+  kf_launch(scale_add_rmsnorm_kernel<TS, TS, TO, TO>, dim3(T), dim3(threads), 0, stream, a, (const TS*)s, x, (const TS*)w, \
+            eps, plus_one, (TO*)out, (TO*)copy, H)
+  if (s_dtype == KF_F32 && out_dtype == KF_F32) KF_GO(float, float);
+  else if (s_dtype == KF_BF16 && out_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (s_dtype == KF_BF16 && out_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
+  else if (s_dtype == KF_F32 && out_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+template <typename TE, typename TO>
+__global__ void side_gate_kernel(const float* __restrict__ gate, const int* __restrict__ tokens, const TE* __restrict__ table,
+                                 int table_ld, int col0, TO* __restrict__ out, int T, int dim) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const long n = (long)T * dim;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long)gridDim.x * blockDim.x) {
+    const long t = idx / dim, j = idx - t * dim;
+    const float e = kf_load(table, (size_t)tokens[t] * table_ld + col0 + j);
+    kf_store(out, idx, kf_act(gate[idx], KF_ACT_GELU_TANH) * e);
+  }
+}
+
+KF_API int kf_side_gate(const float* gate, const int* tokens, const void* table, int table_dtype, int table_ld, int col0,
+                        void* out, int out_dtype, int T, int dim, cudaStream_t stream) {
+  if (T <= 0 || dim <= 0) return KF_OK;
+  const long n = (long)T * dim;
+  const int blocks = (int)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
+#define KF_GO(TE, TO) \
+  kf_launch(side_gate_kernel<TE, TO>, dim3(blocks), dim3(256), 0, stream, gate, tokens, (const TE*)table, table_ld, col0, (TO*)out, T, dim)
+  if (table_dtype == KF_F32 && out_dtype == KF_F32) KF_GO(float, float);
+  else if (table_dtype == KF_BF16 && out_dtype == KF_BF16) KF_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (table_dtype == KF_BF16 && out_dtype == KF_F32) KF_GO(__nv_bfloat16, float);
+  else if (table_dtype == KF_F32 && out_dtype == KF_BF16) KF_GO(float, __nv_bfloat16);
+  else return KF_ERR_DTYPE;
+#undef KF_GO
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}

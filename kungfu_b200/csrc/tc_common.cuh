@@ -150,6 +150,20 @@ __device__ __forceinline__ float act_fast(float x, int act) {
   return kf_act(x, act);
 }
 
+// The gated epilogue: act(gate) * up, or for act == KF_ACT_CLAMPED_SWISH the clamped form some mixtures of experts use,
+//   g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float gated_fast(float g, float u, int act, float limit) {
+  if (act == KF_ACT_CLAMPED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-g * (1.702f * 1.4426950408889634f)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return g * r * (u + 1.f);
+  }
+  return act_fast(g, act) * u;
+}
+
 constexpr int SMEM_LIMIT = 220 * 1024;
 
 // A 2-D map over a row-major [rows, cols] bfloat16 matrix with boxes of [box_rows, 64] and the 128-byte swizzle

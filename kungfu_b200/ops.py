@@ -14,7 +14,7 @@ import threading
 import torch
 
 F32, BF16 = 0, 1
-_ACT = {"gelu_tanh": 0, "gelu_erf": 1, "silu": 2}
+_ACT = {"gelu_tanh": 0, "gelu_erf": 1, "silu": 2, "clamped_swish": 3}      # 3: gated products only, with a limit
 _STATUS = {1: "unsupported combination of element types", 2: "unsupported size", 3: "CUDA launch failed",
            4: "alignment rule broken", 5: "one-time set-up failed"}
 
@@ -361,15 +361,17 @@ def linear(x, weight, out, softcap: float = 0.0) -> None:
 
 
 @_dispatch("linear_gated")
-def linear_gated(x, w_gate_up, out, activation: str, ctx) -> None:
-    """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows."""
+def linear_gated(x, w_gate_up, out, activation: str, ctx, limit: float = 0.0) -> None:
+    """out[T, I] = act(x . Wgate^T) * (x . Wup^T) with w_gate_up = [Wgate; Wup] stacked by rows.  The activation
+    'clamped_swish' is the gated form g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)."""
     T = x.shape[0]
     I = out.shape[1]
-    if out.dtype == torch.bfloat16 and _linear_tc(x, w_gate_up, out, 2, I, 0.0, _ACT[activation]):
+    clamped = activation == "clamped_swish"
+    if out.dtype == torch.bfloat16 and _linear_tc(x, w_gate_up, out, 2, I, float(limit) if clamped else 0.0, _ACT[activation]):
         return
     gu = ctx.buf("ffn_gate_up", (T, 2 * I), torch.float32)
     linear(x, w_gate_up, gu)
-    _check(library().kf_gated_act(_p(gu), _dt(gu), _p(out), _dt(out), T, I, _ACT[activation], _stream()), "gated_act")
+    _check(library().kf_gated_act(_p(gu), _dt(gu), _p(out), _dt(out), T, I, _ACT[activation], _f(limit), _stream()), "gated_act")
 
 
 @_dispatch("linear_act")
@@ -654,6 +656,153 @@ def add2_rmsnorm(a, b, x, *, next_weight=None, next_eps: float = 0.0, next_plus_
     _check(library().kf_add2_rmsnorm(_p(a), _p(b), _p(x), _p(next_weight), _dt(next_weight) if next_weight is not None else F32,
                                      _f(next_eps), int(next_plus_one), _p(next_out),
                                      _dt(next_out) if next_out is not None else F32, T, H, _stream()), "add2_rmsnorm")
+
+
+# ---- the gated delta rule, latent attention, layer scales, per-token side inputs, mixtures of experts ------------------
+
+@_dispatch("linear_cols")
+def linear_cols(base, col0: int, weight, out) -> None:
+    """out[T, N] = base[:, col0:col0 + K] . weight[N, K]^T, `base` a wider 32-bit matrix (the result of a stacked
+    projection): the second half of a factored projection, in 32-bit FMA arithmetic whatever the weights' type."""
+    T, N = out.shape
+    K = weight.shape[1]
+    if base.dtype != torch.float32 or weight.shape[0] != N or base.shape[0] != T:
+        raise KernelError(f"linear_cols: base{tuple(base.shape)} {base.dtype} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    _check(library().kf_linear_simt_cols(_p(base), ctypes.c_long(base.shape[1]), ctypes.c_long(col0), _p(weight), _dt(weight),
+                                         _p(out), _dt(out), T, N, K, _stream()), "linear_cols")
+
+
+@_dispatch("delta_rule")
+def delta_rule(qkv, q0: int, k0: int, v0: int, beta, beta0: int, decay, decay0: int, per_channel: bool, dt_bias, a_log,
+               state, out, heads: int, kv_heads: int, dim: int, vdim: int, ctx, writes: bool = True) -> None:
+    """The gated delta rule over the rows of every request of the step, from and into `state` [requests, heads, dim, vdim]
+    (32-bit): S <- g S (g per head, or per head and key channel = row of S); u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  q, k, v are column ranges of `qkv` (32-bit, after convolution and activation), made unit vectors per head
+    here (q also times dim^-1/2); beta = sigmoid(beta[:, beta0 + h]); g = exp(-exp(a_log[h]) softplus(decay[:, decay0 + ...] +
+    dt_bias)).  Query/key head of head h: h // (heads // kv_heads).  out: 32-bit [rows, heads * vdim]."""
+    _check(library().kf_delta_rule(_p(qkv), qkv.shape[1], int(q0), int(k0), int(v0), _p(beta), beta.shape[1], int(beta0),
+                                   _p(decay), decay.shape[1], int(decay0), int(bool(per_channel)), _p(dt_bias), _p(a_log),
+                                   _dt(a_log), _p(state), _p(out), out.shape[1], heads, kv_heads, dim, vdim, ctx.n_reqs,
+                                   _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), _stream()),
+           "delta_rule")
+
+
+_GATE_ACT = {"silu": 0, "sigmoid": 1}
+
+
+@_dispatch("head_norm_gate")
+def head_norm_gate(o, weight, eps: float, gate, gate0: int, act: str, out, heads: int, vdim: int) -> None:
+    """out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * act(gate[t, gate0 + h * vdim + :]); act silu or sigmoid."""
+    T = out.shape[0]
+    _check(library().kf_head_norm_gate(_p(o), _p(weight), _dt(weight), _f(eps), _p(gate), gate.shape[1], int(gate0),
+                                       _GATE_ACT[act], _p(out), _dt(out), heads, vdim, T, _stream()), "head_norm_gate")
+
+
+@_dispatch("latent_append")
+def latent_append(proj, c0: int, rank: int, weight, eps: float, ctx, cache) -> None:
+    """c = rms_norm(proj[:, c0:c0 + rank]) * weight, written as the key row AND the value row of the single key/value head
+    of `cache` (head size D >= rank, tails zero) at every row's position."""
+    T = proj.shape[0]
+    table = ctx.block_tables[cache.group]
+    D = cache.pages.shape[-1]
+    _check(library().kf_latent_append(_p(proj), proj.shape[1], int(c0), int(rank), _p(weight), _dt(weight), _f(eps),
+                                      _p(ctx.positions), _p(ctx.row_req), _p(table), table.shape[1], cache.page_size,
+                                      _p(cache.pages), _dt(cache.pages), D, T, _stream()), "latent_append")
+
+
+def _grouped(x, x_off, ldx, x_gstride, row_index, row_div, w, w_gstride, out, o_off, ldo, o_gstride, tiles, max_tiles,
+             n_groups, T, N, K, gated, limit, what):
+    tg, tr, tn, nt = tiles if tiles is not None else (None, None, None, None)
+    L = ctypes.c_long
+    _check(library().kf_grouped_linear(_p(x), _dt(x), L(x_off), L(ldx), L(x_gstride), _p(row_index), int(row_div), _p(w),
+                                       _dt(w), L(w_gstride), _p(out), _dt(out), L(o_off), L(ldo), L(o_gstride), _p(tg),
+                                       _p(tr), _p(tn), _p(nt), int(max_tiles), int(n_groups), int(T), int(N), int(K),
+                                       int(gated), _f(limit), _stream()), what)
+
+
+@_dispatch("head_linear")
+def head_linear(x, col0: int, weight, out) -> None:
+    """A linear map per head: out[t, h * O + o] = sum_i x[t, col0 + h * I + i] * weight[h, o, i]; weight [heads, O, I],
+    out [rows, heads * O]; x may be wider than heads * I (a column range of a stacked projection's result)."""
+    H, O, I = weight.shape
+    T = out.shape[0]
+    if out.shape[1] != H * O or x.shape[1] < col0 + H * I:
+        raise KernelError(f"head_linear: x{tuple(x.shape)} from column {col0}, weight{tuple(weight.shape)}, out{tuple(out.shape)} do not agree")
+    _grouped(x, col0, x.shape[1], I, None, 1, weight, O * I, out, 0, out.shape[1], O, None, 0, H, T, O, I, 0, 0.0, "head_linear")
+
+
+@_dispatch("moe_route")
+def moe_route(logits, correction, groups: int, keep: int, top: int, scale: float, ids, weights) -> None:
+    """For every row of 32-bit router logits [T, E]: s = sigmoid(logits); the choice is made on s + correction, among the
+    experts of the `keep` groups (of `groups` equal groups of neighbours) whose two largest choice scores sum highest;
+    ids [T, top] int32 = the `top` largest; weights [T, top] = s of the chosen / (their sum + 1e-20) * scale."""
+    T, E = logits.shape
+    _check(library().kf_moe_route(_p(logits), _p(correction), _dt(correction) if correction is not None else F32, T, E,
+                                  int(groups), int(keep), int(top), _f(scale), _p(ids), _p(weights), _stream()), "moe_route")
+
+
+@_dispatch("moe_plan")
+def moe_plan(ids, n_experts: int, ctx) -> dict:
+    """Lay the (token, choice) pairs of `ids` [T, top] out expert by expert.  Returns the device arrays the grouped
+    products and the combination read: sorted_pair, inverse, and the list of 64-row tiles per expert."""
+    T, top = ids.shape
+    P = T * top
+    max_tiles = P // 64 + n_experts
+    plan = {"pairs": P, "top": top, "max_tiles": max_tiles,
+            "sorted_pair": ctx.buf("moe_sorted", (P,), torch.int32), "inverse": ctx.buf("moe_inverse", (P,), torch.int32),
+            "tile_group": ctx.buf("moe_tile_group", (max_tiles,), torch.int32),
+            "tile_row0": ctx.buf("moe_tile_row0", (max_tiles,), torch.int32),
+            "tile_nrows": ctx.buf("moe_tile_nrows", (max_tiles,), torch.int32),
+            "n_tiles": ctx.buf("moe_n_tiles", (1,), torch.int32)}
+    _check(library().kf_moe_plan(_p(ids), P, int(n_experts), _p(plan["sorted_pair"]), _p(plan["inverse"]), _p(plan["tile_group"]),
+                                 _p(plan["tile_row0"]), _p(plan["tile_nrows"]), _p(plan["n_tiles"]), _stream()), "moe_plan")
+    return plan
+
+
+@_dispatch("moe_linear")
+def moe_linear(x, plan: dict, weight, out, *, gather: bool, gated: bool = False, limit: float = 0.0) -> None:
+    """out[r] = x_r . weight[e(r)]^T for every sorted pair r of the plan, e(r) its expert; weight [E, N (or 2N: gate rows
+    then up rows, when gated), K].  `gather`: x holds one row per TOKEN and pair r reads the row of its token; otherwise
+    x holds one row per sorted pair.  gated: out = the clamped gated activation of (gate, up) with `limit`."""
+    E, NW, K = weight.shape
+    N = NW // 2 if gated else NW
+    if out.shape[0] != plan["pairs"] or out.shape[1] != N or x.shape[1] != K:
+        raise KernelError(f"moe_linear: x{tuple(x.shape)} weight{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    tiles = (plan["tile_group"], plan["tile_row0"], plan["tile_nrows"], plan["n_tiles"])
+    _grouped(x, 0, K, 0, plan["sorted_pair"] if gather else None, plan["top"] if gather else 1, weight, NW * K, out, 0, N, 0,
+             tiles, plan["max_tiles"], E, plan["pairs"], N, K, int(gated), limit, "moe_linear")
+
+
+@_dispatch("moe_combine")
+def moe_combine(expert_out, plan: dict, weights, shared, y) -> None:
+    """y[t] = sum_j weights[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), 32-bit, j ascending."""
+    T, W = y.shape
+    _check(library().kf_moe_combine(_p(expert_out), _p(plan["inverse"]), _p(weights), _p(shared), _p(y), T, W, plan["top"],
+                                    _stream()), "moe_combine")
+
+
+@_dispatch("scale_add_rmsnorm")
+def scale_add_rmsnorm(a, scale, x, *, next_weight=None, next_eps: float = 0.0, next_plus_one: bool = False, next_out=None,
+                      copy_out=None) -> None:
+    """x += a * scale (one factor per column), 32-bit; next_out = rmsnorm(x) * g_next and copy_out = x (in its own element
+    type) in the same pass when given."""
+    T, H = x.shape
+    ref = next_out if next_out is not None else copy_out
+    if next_out is not None and copy_out is not None and next_out.dtype != copy_out.dtype:
+        raise KernelError("scale_add_rmsnorm: next_out and copy_out must share one element type")
+    if next_weight is not None and next_weight.dtype != scale.dtype:
+        raise KernelError("scale_add_rmsnorm: the scale and the next norm's weight must share one element type")
+    _check(library().kf_scale_add_rmsnorm(_p(a), _p(scale), _dt(scale), _p(x), _p(next_weight), _f(next_eps), int(next_plus_one),
+                                          _p(next_out), _p(copy_out), _dt(ref) if ref is not None else F32, T, H, _stream()),
+           "scale_add_rmsnorm")
+
+
+@_dispatch("side_gate")
+def side_gate(gate, tokens, table, col0: int, out) -> None:
+    """out[t, j] = gelu_tanh(gate[t, j]) * table[tokens[t], col0 + j]; gate 32-bit [T, dim]."""
+    T, dim = out.shape
+    _check(library().kf_side_gate(_p(gate), _p(tokens), _p(table), _dt(table), table.shape[1], int(col0), _p(out), _dt(out),
+                                  T, dim, _stream()), "side_gate")
 
 
 @_dispatch("activation")

@@ -7,7 +7,11 @@ from .rope import Rope
 from .conv import ShortConv
 from .attention import ConvGatedAttention, PagedAttention
 from .ssm import Mamba2Mixer
+from .latent import LatentAttention
+from .delta import GatedDeltaMixer
+from .moe import RoutedExperts
+from .side import TokenSide
 from .ffn import DenseFfn, GatedFfn
 from .embedding import Embedding, LmHead
-from .block import ParallelBlock, SandwichBlock
+from .block import ParallelBlock, SandwichBlock, ScaledBlock
 from .model import DecoderModel, LayerCall, default_schedule

@@ -70,3 +70,52 @@ class ParallelBlock(Block):
 
 
 register_block("parallel", ParallelBlock)
+
+
+class ScaledBlock(Block):
+    """A pre-norm block whose branch results are multiplied column by column by a learned scale before they join the
+    residual, with an optional per-token side input after the feed-forward:
+      x <- x + s1 * mixer(norm1(x));   x <- x + s2 * ffn(norm2(x));   x <- x + side_norm(side(x, token))
+    `ffn` and `side` may be None.  Every residual update is one 32-bit kernel that also computes the norm that comes next
+    (this block's second norm, or the next block's first), and, before a side input, the copy of the residual rows in
+    the element type its product takes."""
+    fuses_next_norm = True
+
+    def __init__(self, pre_mixer: RmsNorm, mixer: Mixer, scale_mixer, pre_ffn: RmsNorm | None, ffn: FeedForward | None,
+                 scale_ffn, side=None):
+        self.pre_mixer, self.mixer, self.scale_mixer = pre_mixer, mixer, scale_mixer
+        self.pre_ffn, self.ffn, self.scale_ffn, self.side = pre_ffn, ffn, scale_ffn, side
+
+    @staticmethod
+    def _norm_args(then, ctx, rows, act):
+        if isinstance(then, RmsNorm):
+            out = ctx.buf("norm_out", (rows, then.width), act)
+            return out, dict(next_weight=then.weight, next_eps=then.eps, next_plus_one=then.plus_one, next_out=out)
+        return None, {}
+
+    def forward(self, x, ctx, cache, normed=None, then=None):
+        act = ctx.act_dtype
+        T = x.shape[0]
+        n = normed if normed is not None else self.pre_mixer.forward(x, ctx, act)
+        branch, scale = self.mixer.forward(n, ctx, cache), self.scale_mixer
+        if self.ffn is not None:
+            n2, kw = self._norm_args(self.pre_ffn, ctx, T, act)
+            ops.scale_add_rmsnorm(branch, scale, x, **kw)
+            branch, scale = self.ffn.forward(n2, ctx), self.scale_ffn
+        if self.side is None:
+            nxt, kw = self._norm_args(then, ctx, T, act)
+            ops.scale_add_rmsnorm(branch, scale, x, **kw)
+            if nxt is None and then is not None:
+                nxt = then.forward(x, ctx, act)
+            return x, nxt
+        if act == x.dtype:
+            ops.scale_add_rmsnorm(branch, scale, x)
+            rows = x
+        else:
+            rows = ctx.buf("side_rows", tuple(x.shape), act)
+            ops.scale_add_rmsnorm(branch, scale, x, copy_out=rows)
+        y = self.side.forward(rows, ctx)
+        return x, self.side.norm.add_into(y, x, ctx, then=then, out_dtype=act if then is not None else None)
+
+
+register_block("scaled", ScaledBlock)

@@ -15,13 +15,18 @@ from .. import ops
 from .base import FeedForward, register_feed_forward
 
 ACTIVATIONS = ("gelu_tanh", "gelu_erf", "silu")
+GATED_ACTIVATIONS = ACTIVATIONS + ("clamped_swish",)
 
 
 class GatedFfn(FeedForward):
-    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str = "gelu_tanh"):
-        if activation not in ACTIVATIONS:
-            raise ValueError(f"activation {activation!r} is not one of {ACTIVATIONS}")
-        if w_gate_up.shape[0] != 2 * w_down.shape[1]:
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str = "gelu_tanh", limit: float = 0.0,
+                 out_tag: str = "branch_out"):
+        """`activation` 'clamped_swish' is the gated form g = min(gate, limit), u = clamp(up, -limit, limit),
+        h = g sigmoid(1.702 g) (u + 1) that the experts of some mixtures use (`limit` is read by it alone)."""
+        if activation not in GATED_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {GATED_ACTIVATIONS}")
+        self.limit, self.out_tag = float(limit), out_tag
+        if w_gate_up.dim() == 2 and w_down.dim() == 2 and w_gate_up.shape[0] != 2 * w_down.shape[1]:
             raise ValueError("stacked gate/up matrix must have twice as many rows as the down matrix has columns")
         self.w_gate_up, self.w_down = w_gate_up, w_down
         self.activation = activation
@@ -31,8 +36,11 @@ class GatedFfn(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         h = ctx.buf("ffn_h", (T, self.inner), ctx.act_dtype)
-        ops.linear_gated(x, self.w_gate_up, h, self.activation, ctx)
-        y = ctx.buf("branch_out", (T, self.width), torch.float32)
+        if self.activation == "clamped_swish":
+            ops.linear_gated(x, self.w_gate_up, h, self.activation, ctx, limit=self.limit)
+        else:
+            ops.linear_gated(x, self.w_gate_up, h, self.activation, ctx)
+        y = ctx.buf(self.out_tag, (T, self.width), torch.float32)
         ops.linear(h, self.w_down, y)
         return y
 

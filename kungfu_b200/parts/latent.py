@@ -1,0 +1,78 @@
+"""Attention over a latent: every token leaves one small row c in the cache, and every head's keys and values are linear
+maps of it.
+
+For the normed input x of a token, with H heads, query/key size d, value size dv and latent size r:
+  q_h = W_q,h x                                  c = rms_norm(W_dkv x) * w_c            (only c is cached, in pages)
+  k_h(j) = W_uk,h c_j,  v_h(j) = W_uv,h c_j      s_hj = (q_h . k_h(j)) * scale, causal softmax over j, no positions
+  y = W_o concat_h(sum_j p_hj v_h(j))
+The expansions never happen.  Because q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j and sum_j p_hj W_uv,h c_j =
+W_uv,h (sum_j p_hj c_j), the mixer maps each query into the latent space (one small product per head), runs the
+framework's paged attention with ONE key/value head whose key row and value row are both c_j, and maps each head's
+result back with W_uv,h.  The latent head is padded with zeros to the next size the attention kernels have an instance
+for (the maps' weights are padded likewise, so the padding is exact).  Scores, softmax and the norm of c are 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Mixer, PagedKV, pad_rows, register_mixer
+
+_KERNEL_HEAD_SIZES = (16, 32, 64, 128, 256)
+
+
+def latent_head_size(rank: int) -> int:
+    """The head size the latent is stored with: the smallest the tensor-core attention kernels take that holds `rank`."""
+    for d in _KERNEL_HEAD_SIZES:
+        if rank <= d:
+            return d
+    raise ValueError(f"a latent of {rank} elements is above {_KERNEL_HEAD_SIZES[-1]}, the largest head the attention kernels take")
+
+
+class LatentAttention(Mixer):
+    def __init__(self, w_q: torch.Tensor, w_dkv: torch.Tensor, c_norm: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor,
+                 wo: torch.Tensor, *, n_heads: int, dim: int, vdim: int, rank: int, scale: float, norm_eps: float,
+                 window: int | None = None):
+        self.n_heads, self.dim, self.vdim, self.rank = int(n_heads), int(dim), int(vdim), int(rank)
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.window = None if window is None else int(window)
+        self.head_dim = D = latent_head_size(self.rank)
+        self.width = wo.shape[0]
+        self.c_norm, self.wo = c_norm, wo
+        H, d, dv, r = self.n_heads, self.dim, self.vdim, self.rank
+        if w_q.numel() and w_dkv.numel() and w_uk.numel() and w_uv.numel():
+            # [q | c] from one product; result rows start on 16-byte boundaries
+            self.w_in = pad_rows(torch.cat([w_q, w_dkv], dim=0).contiguous())
+            # W_uk,h^T as a map d -> D (rows beyond r zero) and W_uv,h as a map D -> dv (columns beyond r zero)
+            uk = torch.zeros((H, D, d), dtype=w_uk.dtype, device=w_uk.device)
+            uk[:, :r, :] = w_uk.view(H, d, r).transpose(1, 2)
+            uv = torch.zeros((H, dv, D), dtype=w_uv.dtype, device=w_uv.device)
+            uv[:, :, :r] = w_uv.view(H, dv, r)
+            self.w_uk_t, self.w_uv = uk.contiguous(), uv.contiguous()
+        else:                                              # a fault the weight store has already recorded
+            self.w_in = self.w_uk_t = self.w_uv = torch.empty(0)
+        self.proj_width = max(H * d + r, self.w_in.shape[0])
+        ops.check_attention_sizes(H, 1, D)
+
+    def state_need(self):
+        return PagedKV(1, self.head_dim, self.window)
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        H, D = self.n_heads, self.head_dim
+        proj = ctx.buf("latent_proj", (T, self.proj_width), torch.float32)
+        ops.linear(x, self.w_in, proj)
+        if cache.writes:
+            ops.latent_append(proj, H * self.dim, self.rank, self.c_norm, self.norm_eps, ctx, cache)
+        q = ctx.buf("attn_q", (T, H * D), ctx.act_dtype)
+        ops.head_linear(proj, 0, self.w_uk_t, q)
+        o = ctx.buf("attn_o", (T, H * D), ctx.act_dtype)
+        ops.paged_attention(q, o, ctx, cache, H, 1, D, self.scale, 0.0, self.window)
+        v = ctx.buf("latent_v", (T, H * self.vdim), ctx.act_dtype)
+        ops.head_linear(o, 0, self.w_uv, v)
+        y = ctx.buf("branch_out", (T, self.width), torch.float32)
+        ops.linear(v, self.wo, y)
+        return y
+
+
+register_mixer("latent_attention", LatentAttention)

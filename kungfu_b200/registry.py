@@ -55,6 +55,9 @@ def _register_builtin() -> None:
     from .config.bolonex import BolonexConfig
     from .models import bolonex
     register("Bolonex", BolonexConfig.from_dict, bolonex.build, bolonex.tensor_specs, replace=True)
+    from .config.petanex import PetanexConfig
+    from .models import petanex
+    register("Petanex", PetanexConfig.from_dict, petanex.build, petanex.tensor_specs, replace=True)
 
 
 _register_builtin()

@@ -108,6 +108,10 @@ class WeightStore:
     def has(self, name: str) -> bool:
         return name in self._source
 
+    def shape_of(self, name: str) -> tuple | None:
+        """The stored shape of `name` (None if the source has no such tensor): for sizes that only a tensor's shape gives."""
+        return tuple(self._shapes[name]) if name in self._shapes else None
+
     def take(self, name: str, shape: tuple) -> torch.Tensor:
         """The tensor `name`, which must have `shape`.  A fault is recorded, not raised: `finish()` reports all."""
         shape = tuple(int(s) for s in shape)

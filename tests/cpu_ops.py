@@ -48,10 +48,19 @@ class CpuOps:
             y = softcap * torch.tanh(y / softcap)
         out.copy_(y.to(out.dtype))
 
-    def linear_gated(self, x, w_gate_up, out, activation, ctx):
+    def linear_gated(self, x, w_gate_up, out, activation, ctx, limit=0.0):
         I = out.shape[1]
         gu = x.float() @ w_gate_up.float().T
-        out.copy_((_act(activation, gu[:, :I]) * gu[:, I:]).to(out.dtype))
+        if activation == "clamped_swish":
+            out.copy_(self._clamped(gu[:, :I], gu[:, I:], limit).to(out.dtype))
+        else:
+            out.copy_((_act(activation, gu[:, :I]) * gu[:, I:]).to(out.dtype))
+
+    @staticmethod
+    def _clamped(g, u, limit):
+        g = torch.clamp(g, max=limit)
+        u = torch.clamp(u, min=-limit, max=limit)
+        return g * torch.sigmoid(1.702 * g) * (u + 1.0)
 
     def rope_table(self, positions, inv_freq, cos, sin):
         ang = positions.float()[:, None] * inv_freq[None, :]
@@ -241,6 +250,129 @@ class CpuOps:
         x.add_(a if b is None else a + b)
         if next_out is not None:
             self.rmsnorm(x, next_weight, next_eps, next_plus_one, next_out)
+
+    # ---- gated delta rule, latent attention, layer scales, side inputs, mixtures of experts ---------------------------------
+    def linear_cols(self, base, col0, weight, out):
+        K = weight.shape[1]
+        out.copy_((base[:, col0:col0 + K].float() @ weight.float().T).to(out.dtype))
+
+    def delta_rule(self, qkv, q0, k0, v0, beta, beta0, decay, decay0, per_channel, dt_bias, a_log, state, out, heads, kv_heads,
+                   dim, vdim, ctx, writes=True):
+        rate = torch.exp(a_log.float())
+        rep = heads // kv_heads
+        for req in range(ctx.n_reqs):
+            n = int(ctx.req_n_rows[req])
+            if n <= 0:
+                continue
+            r0, slot = int(ctx.req_row_start[req]), int(ctx.req_state_slot[req])
+            S = state[slot].clone()                                   # [heads, dim, vdim]
+            for i in range(n):
+                row = qkv[r0 + i].float()
+                q = row[q0:q0 + kv_heads * dim].view(kv_heads, dim)
+                k = row[k0:k0 + kv_heads * dim].view(kv_heads, dim)
+                v = row[v0:v0 + heads * vdim].view(heads, vdim)
+                q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+                k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+                b = torch.sigmoid(beta[r0 + i, beta0:beta0 + heads].float())
+                if per_channel:
+                    raw = decay[r0 + i, decay0:decay0 + heads * dim].float() + dt_bias.float()
+                    g = torch.exp(-rate[:, None] * torch.nn.functional.softplus(raw, threshold=20.0).view(heads, dim))
+                else:
+                    raw = decay[r0 + i, decay0:decay0 + heads].float() + dt_bias.float()
+                    g = torch.exp(-rate * torch.nn.functional.softplus(raw, threshold=20.0))[:, None].expand(heads, dim)
+                for h in range(heads):
+                    kh = h // rep
+                    S[h] = S[h] * g[h][:, None]
+                    u = b[h] * (v[h] - S[h].T @ k[kh])
+                    S[h] = S[h] + torch.outer(k[kh], u)
+                    out[r0 + i, h * vdim:(h + 1) * vdim] = S[h].T @ q[kh]
+            if writes:
+                state[slot] = S
+
+    def head_norm_gate(self, o, weight, eps, gate, gate0, act, out, heads, vdim):
+        T = out.shape[0]
+        y = o[:T].float().view(T, heads, vdim)
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight.float()[None, None, :]
+        z = gate[:T, gate0:gate0 + heads * vdim].float().view(T, heads, vdim)
+        y = y * (z * torch.sigmoid(z) if act == "silu" else torch.sigmoid(z))
+        out.copy_(torch.nan_to_num(y).reshape(T, heads * vdim).to(out.dtype))
+
+    def latent_append(self, proj, c0, rank, weight, eps, ctx, cache):
+        table = ctx.block_tables[cache.group]
+        D = cache.pages.shape[-1]
+        for t in range(proj.shape[0]):
+            req = int(ctx.row_req[t])
+            if req < 0:
+                continue
+            c = proj[t, c0:c0 + rank].float()
+            c = c * torch.rsqrt(c.pow(2).mean() + eps) * weight.float()
+            pos = int(ctx.positions[t])
+            page = int(table[req, pos // cache.page_size])
+            row = torch.zeros(D)
+            row[:rank] = c
+            cache.pages[page, 0, 0, pos % cache.page_size] = row.to(cache.pages.dtype)
+            cache.pages[page, 1, 0, pos % cache.page_size] = row.to(cache.pages.dtype)
+
+    def head_linear(self, x, col0, weight, out):
+        H, O, I = weight.shape
+        T = out.shape[0]
+        xs = x[:T, col0:col0 + H * I].float().view(T, H, I)
+        out.copy_(torch.einsum("thi,hoi->tho", xs, weight.float()).reshape(T, H * O).to(out.dtype))
+
+    def moe_route(self, logits, correction, groups, keep, top, scale, ids, weights):
+        T, E = logits.shape
+        s = torch.sigmoid(torch.nan_to_num(logits.float()))
+        choice = s + (correction.float()[None, :] if correction is not None else 0.0)
+        if groups > 1:
+            per = E // groups
+            g = choice.view(T, groups, per)
+            score = g.topk(min(2, per), dim=-1).values.sum(-1)
+            best = score.topk(keep, dim=-1).indices
+            ok = torch.zeros(T, groups, dtype=torch.bool).scatter_(1, best, True)
+            choice = choice.masked_fill(~ok[:, :, None].expand(T, groups, per).reshape(T, E), float("-inf"))
+        pick = choice.topk(top, dim=-1).indices
+        w = s.gather(1, pick)
+        ids.copy_(pick.to(torch.int32))
+        weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20) * scale)
+
+    def moe_plan(self, ids, n_experts, ctx):
+        T, top = ids.shape
+        flat = ids.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel())
+        return {"pairs": T * top, "top": top, "sorted_pair": order.to(torch.int32), "inverse": inverse.to(torch.int32),
+                "expert_of_sorted": flat[order]}
+
+    def moe_linear(self, x, plan, weight, out, *, gather, gated=False, limit=0.0):
+        top = plan["top"]
+        for r in range(plan["pairs"]):
+            e = int(plan["expert_of_sorted"][r])
+            row = x[int(plan["sorted_pair"][r]) // top] if gather else x[r]
+            y = weight[e].float() @ row.float()
+            if gated:
+                N = y.shape[0] // 2
+                y = self._clamped(y[:N], y[N:], limit)
+            out[r] = y.to(out.dtype)
+
+    def moe_combine(self, expert_out, plan, weights, shared, y):
+        T, W = y.shape
+        top = plan["top"]
+        rows = expert_out[plan["inverse"].long()].view(T, top, W)
+        acc = (rows * weights[:, :, None]).sum(1)
+        y.copy_(acc + (shared if shared is not None else 0.0))
+
+    def scale_add_rmsnorm(self, a, scale, x, *, next_weight=None, next_eps=0.0, next_plus_one=False, next_out=None, copy_out=None):
+        x.add_(a * scale.float()[None, :])
+        if copy_out is not None:
+            copy_out.copy_(x.to(copy_out.dtype))
+        if next_out is not None:
+            self.rmsnorm(x, next_weight, next_eps, next_plus_one, next_out)
+
+    def side_gate(self, gate, tokens, table, col0, out):
+        T, dim = out.shape
+        e = table.float()[tokens[:T].long()][:, col0:col0 + dim]
+        out.copy_((_act("gelu_tanh", gate.float()) * e).to(out.dtype))
 
     def activation(self, x, out, act):
         out.copy_(_act(act, x.float()).to(out.dtype))
