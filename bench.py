@@ -6,6 +6,7 @@
     python bench.py --micro attention|prompt-attention|gemm|products|reference
                     (kernels alone, JSON lines; for the summaries in profiles/)
     python bench.py --compare bolonex
+    python bench.py --compare petanex
                     (Bolonex beside Gemma 2 at equal layer sizes: prefill and decode throughput and, per operation, the
                     time of one step against the time its bytes take at the measured copy rate; one JSON line)
 
@@ -520,9 +521,15 @@ def gemma_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
 
 
 def compare_bolonex(args) -> dict:
-    """Prefill (one prompt of --prefill-tokens tokens) and decode (--batch requests at --context tokens) of Bolonex and of
-    Gemma 2 at equal sizes, and per operation the time of one eager step beside the time its bytes would take at the
-    measured copy rate (`x_roofline`: 1.0 = at the roofline)."""
+    return compare_models(args, "bolonex", BOLONEX_SIZES, lambda z: (("bolonex", bolonex_config(z), bolonex_op_bytes),
+                                                                      ("gemma2", gemma_twin_config(z), gemma_op_bytes)))
+
+
+def compare_models(args, label: str, size_table: dict, archs_of) -> dict:
+    """Prefill (one prompt of --prefill-tokens tokens) and decode (--batch requests at --context tokens) of two
+    architectures at equal sizes, and per operation the time of one eager step beside the time its bytes would take at the
+    measured copy rate, or its multiply-adds at the measured bfloat16 rate if that is longer (`x_roofline`: 1.0 = at the
+    roofline).  An operation's entry in the byte tables is a byte count, or (bytes, floating-point operations)."""
     import torch
     from kungfu_b200 import api, ops
     from kungfu_b200.engine import StepEntry
@@ -530,12 +537,12 @@ def compare_bolonex(args) -> dict:
     device = api.require_cuda("cuda:0")
     ops.library()
     T, B, ctx_len = args.prefill_tokens, args.batch, min(args.context, 4096)
-    out = {"impl": "ours", "compare": "bolonex", "peaks": pk_src, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+    out = {"impl": "ours", "compare": label, "peaks": pk_src, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
            "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
            "sizes": {}}
-    for name, z in BOLONEX_SIZES.items():
+    for name, z in size_table.items():
         row = {}
-        for arch, raw, op_bytes in (("bolonex", bolonex_config(z), bolonex_op_bytes), ("gemma2", gemma_twin_config(z), gemma_op_bytes)):
+        for arch, raw, op_bytes in archs_of(z):
             cfg, model = api.random_model(raw, seed=0, dtype="bfloat16", device=device)
             steps, warmup, reps = min(args.steps, 32), max(args.warmup, 3), args.reps
             runner = api.make_runner(cfg, model, dtype="bfloat16", device=device, page_size=api.DEFAULT_PAGE_SIZE,
@@ -581,9 +588,12 @@ def compare_bolonex(args) -> dict:
                 per_op[phase] = {"total_ms": round(total, 3), "ops": {}}
                 for op, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1]):
                     e = {"n": n, "us": round(t * 1e3, 1), "share": round(t / total, 3)}
-                    if op in nbytes and nbytes[op] > 0:
-                        ideal_us = nbytes[op] / (pk["hbm_gbs"] * 1e3)
-                        e["bytes"] = int(nbytes[op])
+                    nb, fl = nbytes.get(op, 0) if isinstance(nbytes.get(op, 0), tuple) else (nbytes.get(op, 0), 0)
+                    if nb > 0:
+                        ideal_us = max(nb / (pk["hbm_gbs"] * 1e3), fl / (pk["bf16_tflops"] * 1e6))
+                        e["bytes"] = int(nb)
+                        if fl:
+                            e["flops"] = int(fl)
                         e["x_roofline"] = round(t * 1e3 / ideal_us, 2)
                     per_op[phase]["ops"][op] = e
             m, sd = mean_sd(pf[1:])
@@ -599,6 +609,69 @@ def compare_bolonex(args) -> dict:
     out["slow_kernel_fallbacks"] = ops.fallbacks()
     ops.raise_on_device_error()
     return out
+
+
+# ---- Petanex beside Bolonex at equal layer sizes (--compare petanex) -------------------------------------------------
+# Eight layers in both: attention over a latent, then a delta rule per key channel, then two delta rules per head (Bolonex:
+# attention, then three state-space layers); feed-forwards alternate between dense and a mixture whose chosen experts and
+# shared expert together have the dense width; every layer has a per-token side input.
+PETANEX_SIZES = {
+    "w2048": dict(BOLONEX_SIZES["w2048"], lat_heads=16, rank=256, d_heads=16, d_kv_heads=8, d_dim=128, d_vdim=128, low=64,
+                  experts=32, top=3, e_groups=4, e_keep=2, side=64),
+    "w4096": dict(BOLONEX_SIZES["w4096"], lat_heads=32, rank=256, d_heads=32, d_kv_heads=16, d_dim=128, d_vdim=128, low=128,
+                  experts=64, top=7, e_groups=8, e_keep=4, side=64),
+}
+
+
+def petanex_config(z: dict) -> dict:
+    lat = {"heads": z["lat_heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": z["rank"], "scale": z["dim"] ** -0.5}
+    dl = {"heads": z["d_heads"], "kv_heads": z["d_kv_heads"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": 4}
+    ch = dict(dl, decay_rank=z["low"], gate_rank=z["low"])
+    eff = z["ff"] // (z["top"] + 1) // 64 * 64
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "shared": {"ff": eff, "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["e_groups"], "keep": z["e_keep"]}}}
+    kinds = ["latent_attention", "channel_delta", "delta", "delta"]
+    layers = [{"type": kinds[i % 4], "mixer": (lat, ch, dl, dl)[i % 4], "mlp": dense if i % 2 == 0 else moe}
+              for i in range(COMPARE_LAYERS)]
+    return {"architecture": "Petanex", "width": z["width"], "vocab": COMPARE_VOCAB, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "token_side": {"dim": z["side"]}, "layers": layers}
+
+
+def petanex_op_bytes(z: dict, T: int, n_reqs: int, keys: int) -> dict:
+    """Bytes (and, for the grouped products, floating-point operations) each operation of one Petanex step must move,
+    summed over the layers that run it."""
+    W, L = z["width"], COMPARE_LAYERS
+    H, d, r = z["lat_heads"], z["dim"], z["rank"]
+    dh, dk, dd, dv, low = z["d_heads"], z["d_kv_heads"], z["d_dim"], z["d_vdim"], z["low"]
+    n_lat, n_ch, n_dl = L // 4, L // 4, L // 2
+    n_rec, n_moe = n_ch + n_dl, L // 2
+    cq = 2 * dk * dd + dh * dv
+    eff = z["ff"] // (z["top"] + 1) // 64 * 64
+    P = T * z["top"]
+    used = min(z["experts"], P)                                   # experts whose weights a step touches, at most
+    return {
+        "latent_append": n_lat * T * (4 * r + 4 * r),
+        "head_linear": (n_lat * (T * H * (4 * d + 2 * r + 2 * r + 2 * d) + 4 * H * d * r), n_lat * 4 * T * H * d * r),
+        "paged_attention": n_lat * (n_reqs * keys * 2 * r * 2 + T * H * r * 4),
+        "short_conv": n_rec * T * cq * 8,
+        "short_conv_commit": n_rec * n_reqs * 3 * cq * 8,
+        "linear_cols": (n_ch * (T * 4 * (2 * low + dh * dd + dh * dv) + 2 * low * (dh * dd + dh * dv)), n_ch * 2 * T * low * (dh * dd + dh * dv)),
+        "delta_rule": n_rec * (T * (cq + dh * dv) * 4 + 2 * n_reqs * dh * dd * dv * 4) + n_ch * T * dh * dd * 4,
+        "head_norm_gate": n_rec * T * dh * dv * 10,
+        "scale_add_rmsnorm": 2 * L * T * W * 14,
+        "add_rmsnorm": L * T * W * 14,
+        "side_gate": L * T * z["side"] * 8,
+        "moe_route": n_moe * T * (z["experts"] * 4 + z["top"] * 8),
+        "moe_plan": n_moe * P * 12,
+        "moe_linear": (n_moe * (used * 3 * eff * W * 2 + P * (2 * W + 4 * eff + 4 * W)), n_moe * 6 * P * eff * W),
+        "moe_combine": n_moe * T * W * (4 * z["top"] + 8),
+    }
+
+
+def compare_petanex(args) -> dict:
+    return compare_models(args, "petanex", PETANEX_SIZES, lambda z: (("petanex", petanex_config(z), petanex_op_bytes),
+                                                                      ("bolonex", bolonex_config(z), bolonex_op_bytes)))
 
 
 def micro_attention() -> int:
@@ -1014,13 +1087,14 @@ def main() -> int:
     ap.add_argument("--only-headline", action="store_true", help="skip the other batch sizes, the mixed steps, 32-bit and the other model sizes")
     ap.add_argument("--micro", choices=["attention", "prompt-attention", "gemm", "products", "qkv-rope", "reference"],
                     help="time kernels alone instead of the model step")
-    ap.add_argument("--compare", choices=["bolonex"],
-                    help="another workload: Bolonex beside Gemma 2 at equal layer sizes (prefill, decode, per-operation rooflines)")
+    ap.add_argument("--compare", choices=["bolonex", "petanex"],
+                    help="another workload: Bolonex beside Gemma 2, or Petanex beside Bolonex, at equal layer sizes (prefill, "
+                         "decode, per-operation rooflines)")
     args = ap.parse_args()
     if args.compare:
         args.warmup = max(args.warmup, 3)
         args.reps = max(args.reps, 1)
-        print(json.dumps(compare_bolonex(args)))
+        print(json.dumps(compare_petanex(args) if args.compare == "petanex" else compare_bolonex(args)))
         return 0
     if args.micro:
         return {"attention": micro_attention, "prompt-attention": micro_prompt_attention, "gemm": micro_gemm,
