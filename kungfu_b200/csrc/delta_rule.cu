@@ -7,15 +7,17 @@
 // with q, k unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^(-1/2), beta = sigmoid(raw),
 // g = exp(-exp(A_log_h) * softplus(raw + dt_bias)).  Query/key head of value head h: h / (heads / kv_heads).
 // Everything here is 32-bit.  The tokens of a request are walked in order with the same arithmetic whatever the step
-// holds of it (one token, a portion, a whole prompt): a token's result depends on the cut only through nothing at all,
-// since the state is carried exactly.
+// holds of it (one token, a portion, a whole prompt), and the state is carried exactly: a token's result does not depend
+// on how the sequence was cut.
 //
-// Work split: a block of 128 threads owns (request, head, 32 value columns).  Thread (c, l) keeps rows
-// l*NR .. l*NR+NR-1 of column c in registers (d <= 4 NR; rows beyond d are zero and stay zero); the four lanes of a
-// column add their partial dot products by two shuffles.  Rows of q, k, the decays, v and beta of R tokens at a time
-// are staged in shared memory, where the unit norms, the sigmoid and the decays (the transcendental work) are done by
-// all threads side by side, so that the serial walk is multiply-adds and shared loads only.  A lane's chunk of a staged
-// row starts every NR + 4 floats: the four lanes of a column then read four different banks with 16-byte loads.
+// Work split: a block of 128 threads owns (request, head, 128 / LANES value columns).  Thread (c, l) keeps rows
+// l*NR .. l*NR+NR-1 of column c in registers (d <= LANES * NR; rows beyond d are zero and stay zero); the LANES lanes of
+// a column add their partial dot products by shuffles, each from two interleaved partial sums so that a chain of
+// dependent multiply-adds is NR / 2 long.  Rows of q, k, the decays, v and beta of R tokens at a time arrive in shared
+// memory by cp.async into one of two stages while the stage before is walked; there the unit norms, the sigmoid and
+// the decays (the transcendental work) are done by all threads side by side, so that the serial walk is multiply-adds
+// and shared loads only.  A lane's chunk of a staged row starts every NR + 4 floats: the lanes of a column then read
+// different banks with 16-byte loads.
 //
 // kf_head_norm_gate follows: every head's o is divided by its root mean square over dv, times a weight vector shared
 // by the heads, times silu or sigmoid of a gate column.
@@ -36,25 +38,33 @@ struct KfDeltaArgs {
 
 __device__ __forceinline__ float kf_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-template <typename TW, int NR>
+__device__ __forceinline__ void kf_cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// NR rows of a column per thread, LANES threads per column (d <= NR * LANES), 128 / LANES columns per block.
+template <typename TW, int NR, int LANES>
 __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
   kf_pdl_trigger();
   kf_pdl_wait();
-  constexpr int R = NR >= 64 ? 8 : 16;
-  constexpr int LS = NR + 4;
-  constexpr int ROW = 4 * LS;
-  __shared__ __align__(16) float q_s[R][ROW];
-  __shared__ __align__(16) float k_s[R][ROW];
-  __shared__ __align__(16) float g_s[R][ROW];
-  __shared__ float v_s[R][32];
-  __shared__ float beta_s[R], g1_s[R];
+  constexpr int CB = 128 / LANES;                // value columns of a block
+  constexpr int R = LANES >= 16 ? 4 : 8;         // tokens staged at a time
+  constexpr int LS = NR + 4;                     // floats between the chunks of two lanes
+  constexpr int ROW = LANES * LS;
+  constexpr int DP = LANES * NR;                 // rows of S the block's threads hold (rows beyond d stay zero)
+  __shared__ __align__(16) float q_s[2][R][ROW];
+  __shared__ __align__(16) float k_s[2][R][ROW];
+  __shared__ __align__(16) float g_s[2][R][ROW];
+  __shared__ float bias_s[ROW];
+  __shared__ float v_s[2][R][CB];
+  __shared__ float beta_s[2][R], g1_s[2][R];
   const int req = blockIdx.x / p.H, h = blockIdx.x - req * p.H;
   const int n = p.req_n_rows[req];
   if (n <= 0) return;
   const int row0 = p.req_row_start[req], slot = p.req_state_slot[req];
   const int kh = h / (p.H / p.KH);
-  const int tid = threadIdx.x, c = tid >> 2, l = tid & 3, lane = tid & 31, warp = tid >> 5;
-  const int col0 = blockIdx.y * 32, col = col0 + c;
+  const int tid = threadIdx.x, c = tid / LANES, l = tid % LANES, lane = tid & 31, warp = tid >> 5;
+  const int col0 = blockIdx.y * CB, col = col0 + c;
   const bool col_ok = col < p.dv;
   const int d = p.d, dv = p.dv;
   float S[NR];
@@ -66,92 +76,109 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
   }
   const float rate = expf(kf_load((const TW*)p.a_log, h));
   const float q_scale = 1.f / sqrtf((float)d);
+  const float bias_h = p.per_channel ? 0.f : kf_load((const TW*)p.dt_bias, h);
+  if (p.per_channel)
+    for (int i = tid; i < DP; i += 128) bias_s[(i / NR) * LS + (i % NR)] = i < d ? kf_load((const TW*)p.dt_bias, h * d + i) : 0.f;
 
-  for (int t0 = 0; t0 < n; t0 += R) {
-    const int nr = min(R, n - t0);
-    __syncthreads();                             // the walk over the rows staged before is over
-    for (int idx = tid; idx < nr * 4 * NR; idx += 128) {
-      const int tt = idx / (4 * NR), i = idx - tt * 4 * NR;
+  // rows t0 .. t0 + nr - 1 of the request, as they stand in global memory, into stage `buf` (asynchronous copies)
+  auto issue = [&](int buf, int t0, int nr) {
+    for (int idx = tid; idx < nr * DP; idx += 128) {
+      const int tt = idx / DP, i = idx - tt * DP;
       const int at = (i / NR) * LS + (i % NR);
       const size_t row = (size_t)(row0 + t0 + tt);
-      const bool in = i < d;
-      q_s[tt][at] = in ? p.qkv[row * p.ld_qkv + p.q0 + kh * d + i] : 0.f;
-      k_s[tt][at] = in ? p.qkv[row * p.ld_qkv + p.k0 + kh * d + i] : 0.f;
-      if (p.per_channel) {
-        float g = 1.f;
-        if (in) {
-          const float raw = p.decay[row * p.ld_decay + p.decay0 + h * d + i] + kf_load((const TW*)p.dt_bias, h * d + i);
-          g = expf(-rate * kf_softplus(raw));
-        }
-        g_s[tt][at] = g;
+      if (i < d) {
+        kf_cp_async4(&q_s[buf][tt][at], p.qkv + row * p.ld_qkv + p.q0 + kh * d + i);
+        kf_cp_async4(&k_s[buf][tt][at], p.qkv + row * p.ld_qkv + p.k0 + kh * d + i);
+        if (p.per_channel) kf_cp_async4(&g_s[buf][tt][at], p.decay + row * p.ld_decay + p.decay0 + h * d + i);
+      } else {
+        q_s[buf][tt][at] = 0.f;
+        k_s[buf][tt][at] = 0.f;
+        g_s[buf][tt][at] = 1e30f;                // a raw decay that gives exp(-rate * 1e30) = 0; the rows it scales are zero
       }
     }
-    for (int idx = tid; idx < nr * 32; idx += 128) {
-      const int tt = idx >> 5, cc = idx & 31;
-      v_s[tt][cc] = (col0 + cc < dv) ? p.qkv[(size_t)(row0 + t0 + tt) * p.ld_qkv + p.v0 + h * dv + col0 + cc] : 0.f;
+    for (int idx = tid; idx < nr * CB; idx += 128) {
+      const int tt = idx / CB, cc = idx - tt * CB;
+      if (col0 + cc < dv) kf_cp_async4(&v_s[buf][tt][cc], p.qkv + (size_t)(row0 + t0 + tt) * p.ld_qkv + p.v0 + h * dv + col0 + cc);
+      else v_s[buf][tt][cc] = 0.f;
     }
     if (tid < nr) {
       const size_t row = (size_t)(row0 + t0 + tid);
-      beta_s[tid] = 1.f / (1.f + expf(-p.beta[row * p.ld_beta + p.beta0 + h]));
-      if (!p.per_channel) {
-        const float raw = p.decay[row * p.ld_decay + p.decay0 + h] + kf_load((const TW*)p.dt_bias, h);
-        g1_s[tid] = expf(-rate * kf_softplus(raw));
-      }
+      kf_cp_async4(&beta_s[buf][tid], p.beta + row * p.ld_beta + p.beta0 + h);
+      if (!p.per_channel) kf_cp_async4(&g1_s[buf][tid], p.decay + row * p.ld_decay + p.decay0 + h);
     }
-    __syncthreads();
-    for (int tt = warp; tt < nr; tt += 4) {        // unit vectors: one warp per staged token
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int n_chunks = (n + R - 1) / R;
+  issue(0, 0, min(R, n));
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int buf = ch & 1, t0 = ch * R, nr = min(R, n - t0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                             // this stage has landed; the walk over the stage before is over
+    if (ch + 1 < n_chunks) issue(buf ^ 1, t0 + R, min(R, n - t0 - R));
+    // unit vectors, decays and beta of the staged rows, by all threads side by side: one warp per token
+    for (int tt = warp; tt < nr; tt += 4) {
       float sq = 0.f, sk = 0.f;
-      for (int i = lane; i < 4 * NR; i += 32) {
+      for (int i = lane; i < DP; i += 32) {
         const int at = (i / NR) * LS + (i % NR);
-        sq = fmaf(q_s[tt][at], q_s[tt][at], sq);
-        sk = fmaf(k_s[tt][at], k_s[tt][at], sk);
+        sq = fmaf(q_s[buf][tt][at], q_s[buf][tt][at], sq);
+        sk = fmaf(k_s[buf][tt][at], k_s[buf][tt][at], sk);
       }
       sq = kf_warp_sum(sq);
       sk = kf_warp_sum(sk);
       const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
-      for (int i = lane; i < 4 * NR; i += 32) {
+      for (int i = lane; i < DP; i += 32) {
         const int at = (i / NR) * LS + (i % NR);
-        q_s[tt][at] *= fq;
-        k_s[tt][at] *= fk;
+        q_s[buf][tt][at] *= fq;
+        k_s[buf][tt][at] *= fk;
+        if (p.per_channel) g_s[buf][tt][at] = expf(-rate * kf_softplus(g_s[buf][tt][at] + bias_s[at]));
+      }
+      if (lane == 0) {
+        beta_s[buf][tt] = 1.f / (1.f + expf(-beta_s[buf][tt]));
+        if (!p.per_channel) g1_s[buf][tt] = expf(-rate * kf_softplus(g1_s[buf][tt] + bias_h));
       }
     }
     __syncthreads();
     for (int tt = 0; tt < nr; ++tt) {              // the walk
-      const float* kq = &k_s[tt][l * LS];
-      const float* qq = &q_s[tt][l * LS];
-      float kv = 0.f;
+      const float* kq = &k_s[buf][tt][l * LS];
+      const float* qq = &q_s[buf][tt][l * LS];
+      float kr[NR];
+      float kva = 0.f, kvb = 0.f;
       if (p.per_channel) {
-        const float* gq = &g_s[tt][l * LS];
+        const float* gq = &g_s[buf][tt][l * LS];
 #pragma unroll
         for (int i = 0; i < NR; i += 4) {
           const float4 g4 = *reinterpret_cast<const float4*>(gq + i);
           const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
           S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
-          kv = fmaf(S[i], k4.x, kv); kv = fmaf(S[i + 1], k4.y, kv); kv = fmaf(S[i + 2], k4.z, kv); kv = fmaf(S[i + 3], k4.w, kv);
+          kva = fmaf(S[i], k4.x, kva); kvb = fmaf(S[i + 1], k4.y, kvb); kva = fmaf(S[i + 2], k4.z, kva); kvb = fmaf(S[i + 3], k4.w, kvb);
         }
       } else {
-        const float g = g1_s[tt];
+        const float g = g1_s[buf][tt];
 #pragma unroll
         for (int i = 0; i < NR; i += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
+          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
           S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-          kv = fmaf(S[i], k4.x, kv); kv = fmaf(S[i + 1], k4.y, kv); kv = fmaf(S[i + 2], k4.z, kv); kv = fmaf(S[i + 3], k4.w, kv);
+          kva = fmaf(S[i], k4.x, kva); kvb = fmaf(S[i + 1], k4.y, kvb); kva = fmaf(S[i + 2], k4.z, kva); kvb = fmaf(S[i + 3], k4.w, kvb);
         }
       }
-      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-      const float u = beta_s[tt] * (v_s[tt][c] - kv);
-      float o = 0.f;
+      float kv = kva + kvb;
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
+      const float u = beta_s[buf][tt] * (v_s[buf][tt][c] - kv);
+      float oa = 0.f, ob = 0.f;
 #pragma unroll
       for (int i = 0; i < NR; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
         const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
-        S[i] = fmaf(k4.x, u, S[i]); S[i + 1] = fmaf(k4.y, u, S[i + 1]);
-        S[i + 2] = fmaf(k4.z, u, S[i + 2]); S[i + 3] = fmaf(k4.w, u, S[i + 3]);
-        o = fmaf(S[i], q4.x, o); o = fmaf(S[i + 1], q4.y, o); o = fmaf(S[i + 2], q4.z, o); o = fmaf(S[i + 3], q4.w, o);
+        S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
+        S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
+        oa = fmaf(S[i], q4.x, oa); ob = fmaf(S[i + 1], q4.y, ob); oa = fmaf(S[i + 2], q4.z, oa); ob = fmaf(S[i + 3], q4.w, ob);
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      float o = oa + ob;
+#pragma unroll
+      for (int sh = 1; sh < LANES; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
       if (l == 0 && col_ok) p.out[(size_t)(row0 + t0 + tt) * p.ld_out + h * dv + col] = o;
     }
   }
@@ -174,13 +201,12 @@ KF_API int kf_delta_rule(const float* qkv, int ld_qkv, int q0, int k0, int v0, c
   if (d < 1 || d > 256 || dv < 1 || H < 1 || KH < 1 || H % KH) return KF_ERR_SIZE;
   KfDeltaArgs p{qkv, ld_qkv, q0, k0, v0, beta, ld_beta, beta0, decay, ld_decay, decay0, per_channel, dt_bias, a_log,
                 state, out, ld_out, H, KH, d, dv, n_reqs, req_row_start, req_n_rows, req_state_slot, writes};
-  const dim3 grid(n_reqs * H, kf_ceil_div(dv, 32));
-#define KF_GO(TW)                                                                                            \
-  do {                                                                                                       \
-    if (d <= 32) kf_launch(delta_rule_kernel<TW, 8>, grid, dim3(128), 0, stream, p);                        \
-    else if (d <= 64) kf_launch(delta_rule_kernel<TW, 16>, grid, dim3(128), 0, stream, p);                  \
-    else if (d <= 128) kf_launch(delta_rule_kernel<TW, 32>, grid, dim3(128), 0, stream, p);                 \
-    else kf_launch(delta_rule_kernel<TW, 64>, grid, dim3(128), 0, stream, p);                               \
+#define KF_GO(TW)                                                                                                        \
+  do {                                                                                                                   \
+    if (d <= 32) kf_launch(delta_rule_kernel<TW, 8, 4>, dim3(n_reqs * H, kf_ceil_div(dv, 32)), dim3(128), 0, stream, p);       \
+    else if (d <= 64) kf_launch(delta_rule_kernel<TW, 16, 4>, dim3(n_reqs * H, kf_ceil_div(dv, 32)), dim3(128), 0, stream, p); \
+    else if (d <= 128) kf_launch(delta_rule_kernel<TW, 16, 8>, dim3(n_reqs * H, kf_ceil_div(dv, 16)), dim3(128), 0, stream, p); \
+    else kf_launch(delta_rule_kernel<TW, 16, 16>, dim3(n_reqs * H, kf_ceil_div(dv, 8)), dim3(128), 0, stream, p);             \
   } while (0)
   if (w_dtype == KF_F32) KF_GO(float);
   else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);

@@ -19,7 +19,7 @@
 //   the row tiles of every expert.  One block; the order inside an expert is whatever the atomics give, which no
 //   result depends on (a pair's output row is computed from its own row alone).
 // kf_moe_combine: y[t] = sum_j weight[t, j] * expert_out[inverse[t * top + j]] (+ shared[t]), j ascending.
-#include "common.cuh"
+#include "mma_tiles.cuh"
 
 constexpr int GM = 64, GN = 64, GK = 16;
 
@@ -115,6 +115,139 @@ __global__ void __launch_bounds__(256) grouped_simt_kernel(KfGroupedArgs p) {
   }
 }
 
+// The same products on the tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit accumulators) for bfloat16 weights:
+// a block of eight warps owns 64 rows x 128 weight rows (gated: 64 gate rows and the 64 up rows of the same features, so
+// that the warp that holds a gate value also holds its up value and the activation needs no exchange), K in slices of 32
+// through a ring of three stages filled by 16-byte cp.async copies (32-bit rows are converted on their way into shared
+// memory instead).  Shared rows are 40 elements apart: the eight rows and four column pairs a fragment load touches fall
+// into 32 different banks.  A row's sums do not depend on the other rows of its tile.
+constexpr int TM = 64, TN = 128, TK = 32, TSTAGES = 3, TLD = TK + 8;
+
+template <typename TX, typename TO, int GATED>
+__global__ void __launch_bounds__(256) grouped_mma_kernel(KfGroupedArgs p) {
+  using namespace kf_mma;
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 xs[TSTAGES][TM][TLD];
+  __shared__ __align__(16) __nv_bfloat16 ws[TSTAGES][TN][TLD];
+  __shared__ int src_row[TM];
+  int g, r0, nrows;
+  if (p.tile_group) {
+    const int ti = blockIdx.y;
+    if (ti >= *p.n_tiles) return;
+    g = p.tile_group[ti]; r0 = p.tile_row0[ti]; nrows = p.tile_nrows[ti];
+  } else {
+    g = blockIdx.z; r0 = blockIdx.y * TM; nrows = min(TM, p.T - r0);
+  }
+  constexpr int NOUT = GATED ? TN / 2 : TN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+  const int wm = warp >> 2, wn = warp & 3;
+  const int col0 = blockIdx.x * NOUT;
+  const int N = p.N, K = p.K;
+  if (tid < TM) src_row[tid] = tid < nrows ? (p.row_index ? p.row_index[r0 + tid] / p.row_div : r0 + tid) : -1;
+  __syncthreads();
+  const TX* x = (const TX*)p.x + (size_t)g * p.x_gstride;
+  const __nv_bfloat16* w = (const __nv_bfloat16*)p.w + (size_t)g * p.w_gstride;
+
+  auto load_stage = [&](int s, int k0) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {                     // weights: 128 rows x 4 chunks of 8 elements
+      const int idx = tid + it * 256, r = idx >> 2, c = idx & 3;
+      const int feat = col0 + (GATED ? (r & 63) : r);
+      const size_t wrow = GATED && r >= 64 ? (size_t)N + feat : (size_t)feat;
+      const bool ok = feat < N && k0 + c * 8 < K;
+      cp_async16(&ws[s][r][c * 8], w + (ok ? wrow * K + k0 + c * 8 : 0), ok);
+    }
+    const int r = tid >> 2, c = tid & 3, sr = src_row[r];
+    if (sizeof(TX) == 2) {
+      const bool ok = sr >= 0 && k0 + c * 8 < K;
+      cp_async16(&xs[s][r][c * 8], (const __nv_bfloat16*)x + (ok ? (size_t)sr * p.ldx + k0 + c * 8 : 0), ok);
+    } else {
+      uint32_t v[4] = {0u, 0u, 0u, 0u};
+      if (sr >= 0 && k0 + c * 8 < K) {                   // K is a multiple of 8: the chunk is whole
+        const float* src = (const float*)x + (size_t)sr * p.ldx + k0 + c * 8;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = pack_bf16(src[2 * u], src[2 * u + 1]);
+      }
+      *reinterpret_cast<uint4*>(&xs[s][r][c * 8]) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][b][c] = 0.f;
+  const int nk = (K + TK - 1) / TK;
+#pragma unroll
+  for (int s = 0; s < TSTAGES - 1; ++s) {
+    if (s < nk) load_stage(s, s * TK);
+    cp_async_commit();
+  }
+  // weight row (inside the tile) of this warp's n-tile nt
+  int wrow_of[4];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) wrow_of[nt] = GATED ? (nt < 2 ? wn * 16 + nt * 8 : 64 + wn * 16 + (nt - 2) * 8) : wn * 32 + nt * 8;
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<TSTAGES - 2>();
+    __syncthreads();
+    if (kt + TSTAGES - 1 < nk) load_stage((kt + TSTAGES - 1) % TSTAGES, (kt + TSTAGES - 1) * TK);
+    cp_async_commit();
+    const int s = kt % TSTAGES;
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t a[2][4], b[4][2];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        const __nv_bfloat16* base = &xs[s][wm * 32 + mi * 16 + gid][kk + 2 * tig];
+        a[mi][0] = *reinterpret_cast<const uint32_t*>(base);
+        a[mi][1] = *reinterpret_cast<const uint32_t*>(base + 8 * TLD);
+        a[mi][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+        a[mi][3] = *reinterpret_cast<const uint32_t*>(base + 8 * TLD + 8);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const __nv_bfloat16* base = &ws[s][wrow_of[nt] + gid][kk + 2 * tig];
+        b[nt][0] = *reinterpret_cast<const uint32_t*>(base);
+        b[nt][1] = *reinterpret_cast<const uint32_t*>(base + 8);
+      }
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mma_bf16(acc[mi][nt], a[mi], b[nt][0], b[nt][1]);
+    }
+  }
+  cp_async_wait<0>();
+  TO* out = (TO*)p.out + (size_t)g * p.o_gstride;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int nt = 0; nt < (GATED ? 2 : 4); ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = wm * 32 + mi * 16 + gid + (i >= 2 ? 8 : 0);
+        const int c = col0 + (GATED ? wn * 16 + nt * 8 : wn * 32 + nt * 8) + 2 * tig + (i & 1);
+        if (r >= nrows || c >= N) continue;
+        const float v = GATED ? kf_clamped_swish(acc[mi][nt][i], acc[mi][nt + 2][i], p.limit) : acc[mi][nt][i];
+        kf_store(out, (size_t)(r0 + r) * p.ldo + c, v);
+      }
+}
+
+template <typename TX, typename TO>
+static int grouped_mma_go(const KfGroupedArgs& p, int max_tiles, int n_groups, cudaStream_t s) {
+  const int nout = p.gated ? TN / 2 : TN;
+  const dim3 grid(kf_ceil_div(p.N, nout), p.tile_group ? max_tiles : kf_ceil_div(p.T, TM), p.tile_group ? 1 : n_groups);
+  if (p.gated) kf_launch(grouped_mma_kernel<TX, TO, 1>, grid, dim3(256), 0, s, p);
+  else kf_launch(grouped_mma_kernel<TX, TO, 0>, grid, dim3(256), 0, s, p);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
+
+static int g_grouped_tensor_cores = 1;
+KF_API void kf_grouped_use_tensor_cores(int on) { g_grouped_tensor_cores = on; }
+
 template <typename TX, typename TW, typename TO>
 static int grouped_go(const KfGroupedArgs& p, dim3 grid, cudaStream_t s) {
   if (p.gated) kf_launch(grouped_simt_kernel<TX, TW, TO, 1>, grid, dim3(256), 0, s, p);
@@ -135,6 +268,16 @@ KF_API int kf_grouped_linear(const void* x, int x_dtype, long x_off, long ldx, l
   const size_t xe = x_dtype == KF_F32 ? 4 : 2, oe = out_dtype == KF_F32 ? 4 : 2;
   KfGroupedArgs p{(const char*)x + x_off * xe, ldx, x_gstride, row_index, row_div > 0 ? row_div : 1, w, w_gstride,
                   (char*)out + o_off * oe, ldo, o_gstride, tile_group, tile_row0, tile_nrows, n_tiles, T, N, K, gated, limit};
+  // bfloat16 weights whose rows, groups and bases fall on 16-byte boundaries run on the tensor cores; their row tiles are
+  // the plan's 64 rows (GM == TM)
+  const bool w_ok = w_dtype == KF_BF16 && K % 8 == 0 && w_gstride % 8 == 0 && ((uintptr_t)w & 15) == 0;
+  const bool x_ok = x_dtype == KF_F32 || (ldx % 8 == 0 && x_gstride % 8 == 0 && x_off % 8 == 0 && ((uintptr_t)x & 15) == 0);
+  if (g_grouped_tensor_cores && w_ok && x_ok) {
+    if (x_dtype == KF_BF16 && out_dtype == KF_BF16) return grouped_mma_go<__nv_bfloat16, __nv_bfloat16>(p, max_tiles, n_groups, stream);
+    if (x_dtype == KF_BF16 && out_dtype == KF_F32) return grouped_mma_go<__nv_bfloat16, float>(p, max_tiles, n_groups, stream);
+    if (x_dtype == KF_F32 && out_dtype == KF_BF16) return grouped_mma_go<float, __nv_bfloat16>(p, max_tiles, n_groups, stream);
+    if (x_dtype == KF_F32 && out_dtype == KF_F32) return grouped_mma_go<float, float>(p, max_tiles, n_groups, stream);
+  }
   const dim3 grid(kf_ceil_div(N, GN), tile_group ? max_tiles : kf_ceil_div(T, GM), tile_group ? 1 : n_groups);
 #define KF_CASE(XD, WD, OD, TX, TW, TO) \
   if (x_dtype == XD && w_dtype == WD && out_dtype == OD) return grouped_go<TX, TW, TO>(p, grid, stream)

@@ -720,6 +720,12 @@ def _grouped(x, x_off, ldx, x_gstride, row_index, row_div, w, w_gstride, out, o_
                                        int(gated), _f(limit), _stream()), what)
 
 
+def grouped_on_tensor_cores(on: bool) -> None:
+    """False: grouped products (per-head maps, experts) with bfloat16 weights run the generic 32-bit FMA kernel too
+    (tests reach it that way)."""
+    library().kf_grouped_use_tensor_cores(int(bool(on)))
+
+
 @_dispatch("head_linear")
 def head_linear(x, col0: int, weight, out) -> None:
     """A linear map per head: out[t, h * O + o] = sum_i x[t, col0 + h * I + i] * weight[h, o, i]; weight [heads, O, I],

@@ -77,19 +77,19 @@ def unit(x):
     return x / torch.sqrt(x.pow(2).sum(-1, keepdim=True) + 1e-6)
 
 
-def delta_rule(q, k, v, beta, decay):
+def delta_rule(q, k, v, beta, decay, state=None, return_state=False):
     """q, k [T, H, d] (already per value head), v [T, H, dv], beta [T, H], decay [T, H, d] (rows of S by key channel).
     S <- decay * S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
     T, H, d = q.shape
     dv = v.shape[-1]
-    S = torch.zeros(H, d, dv, dtype=DT)
+    S = torch.zeros(H, d, dv, dtype=DT) if state is None else state.clone()
     out = torch.zeros(T, H, dv, dtype=DT)
     for i in range(T):
         S = S * decay[i][:, :, None]
         u = beta[i][:, None] * (v[i] - torch.einsum("hdv,hd->hv", S, k[i]))
         S = S + k[i][:, :, None] * u[:, None, :]
         out[i] = torch.einsum("hdv,hd->hv", S, q[i])
-    return out
+    return (out, S) if return_state else out
 
 
 def delta_mixer(h, m, t, p, eps, per_channel):

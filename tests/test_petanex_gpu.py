@@ -1,0 +1,483 @@
+"""Petanex on the GPU against the plain implementation (tests/plain_petanex.py, float64, whole sequences).
+
+First the new kernels alone on hand-made steps of several requests (some with earlier tokens in their state, one padding
+row), then every mixer alone as a one-layer model, then whole models through the step function in every way of cutting
+the work, in 32-bit on sharp weights and in bfloat16; then long decoding, far keys, used-again slots, generation
+through the engine, and the programs in bin/.
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import petanex_cases as px
+import plain_petanex as pp
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 2e-4, "bfloat16": 4e-2}
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+class FakeStep:
+    """The integers a step's kernels read, for requests of `rows` rows in state slots `slots`; one padding row (request -1)
+    at the end and one request slot without rows."""
+
+    def __init__(self, rows=(5, 1, 3), slots=(2, 0, 3)):
+        self.rows, self.slots = rows, slots
+        row_req, start = [], []
+        for r, n in enumerate(rows):
+            start.append(len(row_req))
+            row_req += [r] * n
+        row_req.append(-1)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        self.n_rows, self.n_reqs = len(row_req), len(rows) + 1
+        self.row_req = i32(row_req)
+        self.req_row_start, self.req_n_rows = i32(start + [0]), i32(list(rows) + [0])
+        self.req_state_slot = i32(list(slots) + [0])
+        self.act_dtype = torch.float32
+        self.starts = start
+
+    def buf(self, tag, shape, dtype):
+        return torch.empty(shape, dtype=dtype, device=DEV)
+
+    def real_rows(self, r):
+        return slice(self.starts[r], self.starts[r] + self.rows[r])
+
+
+def _rel(a, b):
+    return float((a.double().cpu() - b.double().cpu()).abs().max()) / max(float(b.double().abs().max()), 1e-30)
+
+
+# ---- the kernels alone -----------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KH,d,dv,per_channel", [(4, 2, 16, 24, False), (3, 3, 8, 12, True), (1, 1, 40, 33, False),
+                                                   (4, 1, 20, 10, True), (2, 1, 136, 20, True), (4, 2, 64, 64, False),
+                                                   (2, 2, 128, 64, True)])
+def test_delta_rule_in_portions_and_token_by_token(wdtype, H, KH, d, dv, per_channel):
+    """Three requests with earlier tokens in their states run a portion each, then each of them single tokens; the slot of
+    nobody and the padding row stay as they are."""
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(H * 1000 + d)
+    before, rows, tail = (0, 7, 20), (5, 1, 19), 3
+    C = 2 * KH * d + H * dv
+    ld, q0 = C + 3, 3
+    na = H * d if per_channel else H
+    hist = [torch.randn(b + n + tail, ld, generator=g) for b, n in zip(before, rows)]
+    beta = [torch.randn(h.shape[0], H + 2, generator=g) for h in hist]
+    dec = [torch.randn(h.shape[0], na + 1, generator=g) for h in hist]
+    a_log = (-2.0 + torch.rand(H, generator=g)).to(DTYPES[wdtype])
+    dt_bias = (0.5 * torch.randn(na, generator=g)).to(DTYPES[wdtype])
+
+    def plain(i, upto):
+        T = upto
+        x = hist[i][:T].double()
+        q = x[:, q0:q0 + KH * d].view(T, KH, d)
+        k = x[:, q0 + KH * d:q0 + 2 * KH * d].view(T, KH, d)
+        v = x[:, q0 + 2 * KH * d:q0 + C].view(T, H, dv)
+        q, k = pp.unit(q) * d ** -0.5, pp.unit(k)
+        q, k = q.repeat_interleave(H // KH, 1), k.repeat_interleave(H // KH, 1)
+        b = pp.sigmoid(beta[i][:T, 2:].double())
+        raw = dec[i][:T, 1:].double() + dt_bias.double()
+        rate = torch.exp(a_log.double())
+        if per_channel:
+            gd = torch.exp(-rate[None, :, None] * pp.softplus(raw).view(T, H, d))
+        else:
+            gd = torch.exp(-rate[None, :] * pp.softplus(raw))[:, :, None].expand(T, H, d)
+        return pp.delta_rule(q, k, v, b, gd, return_state=True)
+
+    state = torch.full((4, H, d, dv), 9.0)
+    slots = (2, 0, 3)
+    for i, b in enumerate(before):
+        state[slots[i]] = plain(i, b)[1].float() if b else 0.0
+    state = state.to(DEV)
+    st = FakeStep(rows, slots)
+    cat = lambda xs, w: torch.cat([x[b:b + n] for x, b, n in zip(xs, before, rows)] + [torch.zeros(1, w)]).to(DEV)
+    out = torch.full((st.n_rows, H * dv), 5.0, device=DEV)
+    ops.delta_rule(cat(hist, ld), q0, q0 + KH * d, q0 + 2 * KH * d, cat(beta, H + 2), 2, cat(dec, na + 1), 1, per_channel,
+                   dt_bias.to(DEV), a_log.to(DEV), state, out, H, KH, d, dv, st)
+    for i, (b, n) in enumerate(zip(before, rows)):
+        o, S = plain(i, b + n)
+        assert _rel(out[st.real_rows(i)], o[b:].reshape(n, H * dv)) < 2e-5
+        assert _rel(state[slots[i]], S) < 2e-5
+    assert float(state[1].min()) == 9.0 and float(out[-1].min()) == 5.0
+    for j in range(tail):                                            # single rows: what a decode step is
+        st1 = FakeStep((1, 1, 1), slots)
+        at = [b + n + j for b, n in zip(before, rows)]
+        one = lambda xs, w: torch.cat([x[a:a + 1] for x, a in zip(xs, at)] + [torch.zeros(1, w)]).to(DEV)
+        out1 = torch.empty(4, H * dv, device=DEV)
+        ops.delta_rule(one(hist, ld), q0, q0 + KH * d, q0 + 2 * KH * d, one(beta, H + 2), 2, one(dec, na + 1), 1, per_channel,
+                       dt_bias.to(DEV), a_log.to(DEV), state, out1, H, KH, d, dv, st1)
+        for i in range(3):
+            assert _rel(out1[i], plain(i, at[i] + 1)[0][-1].reshape(-1)) < 3e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,dv,act", [(4, 24, "silu"), (3, 12, "sigmoid"), (1, 33, "silu"), (8, 128, "sigmoid")])
+def test_head_norm_and_gate(dtype, H, dv, act):
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(H + dv)
+    o = 3.0 * torch.randn(7, H * dv, generator=g)
+    gate = 2.0 * torch.randn(7, H * dv + 5, generator=g)
+    w = (1.0 + 0.3 * torch.randn(dv, generator=g)).to(DTYPES[dtype])
+    out = torch.empty(7, H * dv, dtype=DTYPES[dtype], device=DEV)
+    ops.head_norm_gate(o.to(DEV), w.to(DEV), 1e-5, gate.to(DEV), 3, act, out, H, dv)
+    z = gate[:, 3:3 + H * dv].double()
+    ref = (pp.rms(o.double().view(7, H, dv), 1e-5) * w.double()).reshape(7, H * dv) * (pp.silu(z) if act == "silu" else pp.sigmoid(z))
+    assert _rel(out, ref) < (1e-5 if dtype == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("E,G,keep,top", [(8, 4, 2, 2), (6, 1, 1, 3), (5, 1, 1, 1), (12, 3, 1, 4), (16, 4, 2, 4), (64, 8, 4, 7), (40, 40, 3, 2)])
+def test_router_against_the_plain_choice(E, G, keep, top):
+    from kungfu_b200 import ops
+    g = torch.Generator().manual_seed(E * 10 + top)
+    T = 133
+    logits = 2.0 * torch.randn(T, E, generator=g)
+    corr = 0.3 * torch.randn(E, generator=g)
+    ids = torch.empty(T, top, dtype=torch.int32, device=DEV)
+    w = torch.empty(T, top, device=DEV)
+    ops.moe_route(logits.to(DEV), corr.to(DEV), G, keep, top, 2.5, ids, w)
+    f = {"router": {"experts": E, "top": top, "scale": 2.5, "groups": {"count": G, "keep": keep}}}
+    rid, rw = pp.route(logits.double(), f, {"p.router": torch.eye(E), "p.correction": corr}, "p.")
+    got = [dict(zip(a.tolist(), b.tolist())) for a, b in zip(ids.cpu(), w.cpu())]
+    for t in range(T):
+        want = dict(zip(rid[t].tolist(), rw[t].tolist()))
+        assert set(got[t]) == set(want), t
+        assert all(abs(got[t][e] - want[e]) < 1e-5 for e in want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "bfloat16 without tensor cores"])
+@pytest.mark.parametrize("T,E,top,W,ff", [(1, 8, 2, 64, 32), (37, 6, 3, 100, 30), (300, 16, 4, 512, 256), (9, 64, 7, 256, 96),
+                                          (130, 3, 2, 200, 72)])
+def test_experts_as_grouped_products(dtype, T, E, top, W, ff):
+    """Plan, both grouped products (tensor-core and generic kernel) and the weighted sum against a loop over tokens and
+    choices."""
+    from kungfu_b200 import ops
+    ops.grouped_on_tensor_cores("without" not in dtype)
+    dtype = dtype.split()[0]
+    st = FakeStep()
+    tdt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, W, generator=g).to(tdt)
+    wgu = (torch.randn(E, 2 * ff, W, generator=g) / W ** 0.5 * 2).to(tdt)
+    wd = (torch.randn(E, W, ff, generator=g) / ff ** 0.5).to(tdt)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, top, generator=g)
+    shared = torch.randn(T, W, generator=g)
+    plan = ops.moe_plan(ids.to(DEV), E, st)
+    h = torch.empty(T * top, ff, dtype=tdt, device=DEV)
+    ops.moe_linear(x.to(DEV), plan, wgu.to(DEV), h, gather=True, gated=True, limit=1.2)
+    eo = torch.empty(T * top, W, device=DEV)
+    ops.moe_linear(h, plan, wd.to(DEV), eo, gather=False)
+    y = torch.empty(T, W, device=DEV)
+    ops.moe_combine(eo, plan, wts.to(DEV), shared.to(DEV), y)
+    ref = shared.double().clone()
+    for t in range(T):
+        for j in range(top):
+            e = int(ids[t, j])
+            gu = wgu[e].double() @ x[t].double()
+            gt, up = torch.clamp(gu[:ff], max=1.2), torch.clamp(gu[ff:], -1.2, 1.2)
+            hid = gt * pp.sigmoid(1.702 * gt) * (up + 1.0)
+            if dtype == "bfloat16":
+                hid = hid.to(torch.bfloat16).double()
+            ref[t] += float(wts[t, j]) * (wd[e].double() @ hid)
+    ops.grouped_on_tensor_cores(True)
+    assert _rel(y, ref) < (2e-5 if dtype == "float32" else 1e-2)
+    inv = plan["inverse"].cpu().long()
+    assert sorted(inv.tolist()) == list(range(T * top))
+    assert torch.equal(plan["sorted_pair"].cpu().long()[inv], torch.arange(T * top))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,K,I", [(5, 64, 96), (70, 512, 1024), (300, 512, 1024), (600, 1024, 512), (3, 100, 70)])
+def test_clamped_gated_feed_forward_in_every_launch_shape(dtype, T, K, I):
+    from kungfu_b200 import ops
+    st = FakeStep()
+    g = torch.Generator().manual_seed(T + K)
+    x = torch.randn(T, K, generator=g).to(DTYPES[dtype])
+    w = (torch.randn(2 * I, K, generator=g) / K ** 0.5 * 2.0).to(DTYPES[dtype])
+    out = torch.empty(T, I, dtype=DTYPES[dtype], device=DEV)
+    ops.linear_gated(x.to(DEV), w.to(DEV), out, "clamped_swish", st, limit=1.5)
+    gu = x.double() @ w.double().T
+    gt, up = torch.clamp(gu[:, :I], max=1.5), torch.clamp(gu[:, I:], -1.5, 1.5)
+    assert _rel(out, gt * pp.sigmoid(1.702 * gt) * (up + 1.0)) < (1e-5 if dtype == "float32" else 1e-2)
+    ops.raise_on_device_error(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_row_kernels(dtype):
+    """Scaled residual update with the next norm and a copy; the side input's gate; per-head maps; a product over a column
+    range."""
+    from kungfu_b200 import ops
+    tdt = DTYPES[dtype]
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    g = torch.Generator().manual_seed(3)
+    for H in (64, 100, 2304):
+        a, x = torch.randn(7, H, generator=g), torch.randn(7, H, generator=g)
+        s, w = (0.6 + 0.2 * torch.randn(H, generator=g)).to(tdt), (1 + 0.1 * torch.randn(H, generator=g)).to(tdt)
+        xd, nxt, cp = x.to(DEV), torch.empty(7, H, dtype=tdt, device=DEV), torch.empty(7, H, dtype=tdt, device=DEV)
+        ops.scale_add_rmsnorm(a.to(DEV), s.to(DEV), xd, next_weight=w.to(DEV), next_eps=1e-5, next_out=nxt, copy_out=cp)
+        ref = x.double() + a.double() * s.double()
+        assert _rel(xd, ref) < 1e-6 and _rel(cp, ref) < tol and _rel(nxt, pp.norm(ref, w, 1e-5)) < tol
+        x2 = x.to(DEV)
+        ops.scale_add_rmsnorm(a.to(DEV), s.to(DEV), x2)
+        assert _rel(x2, ref) < 1e-6
+    gate, table = torch.randn(9, 5, generator=g), torch.randn(30, 23, generator=g).to(tdt)
+    tok = torch.randint(0, 30, (9,), generator=g).to(torch.int32)
+    out = torch.empty(9, 5, dtype=tdt, device=DEV)
+    ops.side_gate(gate.to(DEV), tok.to(DEV), table.to(DEV), 11, out)
+    assert _rel(out, pp.gelu_tanh(gate.double()) * table.double()[tok.long()][:, 11:16]) < tol
+    for Hh, I, O, col0, extra in ((4, 16, 32, 0, 20), (20, 12, 64, 4, 33), (3, 64, 24, 0, 0)):
+        x = torch.randn(70, col0 + Hh * I + extra, generator=g)
+        w = (torch.randn(Hh, O, I, generator=g) / I ** 0.5).to(tdt)
+        out = torch.empty(70, Hh * O, dtype=tdt, device=DEV)
+        ops.head_linear(x.to(DEV), col0, w.to(DEV), out)
+        ref = torch.einsum("thi,hoi->tho", x[:, col0:col0 + Hh * I].double().view(70, Hh, I), w.double()).reshape(70, Hh * O)
+        assert _rel(out, ref) < tol
+    base, w = torch.randn(70, 90, generator=g), (torch.randn(50, 7, generator=g)).to(tdt)
+    out = torch.empty(70, 50, device=DEV)
+    ops.linear_cols(base.to(DEV), 81, w.to(DEV), out)
+    assert _rel(out, base[:, 81:88].double() @ w.double().T) < 1e-5
+
+
+# ---- the model through the step function -------------------------------------------------------------------------
+
+def _runner(folder, dtype, page, max_tokens, max_requests=4, graphs=True, ctx=2048):
+    from kungfu_b200 import api
+    cfg, model = api.load_model(folder, dtype=dtype, device=DEV)
+    return api.make_runner(cfg, model, dtype=dtype, device=DEV, page_size=page, max_tokens=max_tokens,
+                           max_requests=max_requests, max_context=ctx, cuda_graphs=graphs)
+
+
+def _check(got, ref, tol):
+    """32-bit: the largest difference of any logit against the largest logit, below `tol` at every place.  bfloat16: per
+    place, the root mean square of the differences against that of the place's logits, bounded as a distribution (small
+    random models amplify 8-bit rounding unevenly): half of the places within tol / 2, nineteen in twenty within 2 tol,
+    and all but three in a hundred within 0.5.  Those three: where two experts' choice scores are a close call, 8-bit
+    rounding of the router's input can make the choice fall the other way, which changes that place by order 1 and,
+    through the states, some places after it; the 32-bit runs on sharp weights are the strict comparison."""
+    assert got
+    if tol < 1e-2:
+        scale = max(float(r.abs().max()) for r in ref.values())
+        worst = max(float((row - ref[rid][pos]).abs().max()) for (rid, pos), row in got.items()) / scale
+        assert worst < tol, f"rel err {worst:.3e}"
+        return
+    errs = sorted(float((row - ref[rid][pos]).pow(2).mean().sqrt() / ref[rid][pos].pow(2).mean().sqrt())
+                  for (rid, pos), row in got.items())
+    mid, high, top = errs[len(errs) // 2], errs[min(len(errs) - 1, (len(errs) * 19) // 20)], errs[min(len(errs) - 1, (len(errs) * 97) // 100)]
+    assert mid < tol / 2 and high < 2 * tol and top < 0.5, f"rel err median {mid:.3e}, 95 % {high:.3e}, 97 % {top:.3e}"
+
+
+ONE_LAYER = {
+    "latent": px.config(64, 200, [px.layer("latent_attention", px.latent(4, 16, 24, 20, 0.3))], scale=2.0),
+    "latent_wide": px.config(128, 200, [px.layer("latent_attention", px.latent(20, 32, 16, 128, 0.2))]),
+    "delta": px.config(64, 200, [px.layer("delta", px.delta(4, 2, 16, 24, 3))], scale=2.0),
+    "channel_delta": px.config(64, 200, [px.layer("channel_delta", px.delta(3, 3, 8, 12, 2))], scale=2.0),
+    "moe": px.config(64, 200, [px.layer("delta", px.delta(1, 1, 8, 8, 1), px.moe(8, 3, 32, 1.0, 2.0, groups=(2, 1), shared=(16, 0.5)))]),
+    "side": px.config(64, 200, [px.layer("delta", px.delta(1, 1, 8, 8, 2), px.dense(32))], side=6),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", sorted(ONE_LAYER))
+def test_each_mechanism_alone_as_a_one_layer_model(which, dtype, tmp_path):
+    cfg = ONE_LAYER[which]
+    folder = px.write_model(str(tmp_path / "m"), cfg, seed=7, sharp=True)
+    reqs = {"a": helpers.random_tokens(150, cfg["vocab"], 1), "b": helpers.random_tokens(9, cfg["vocab"], 2)}
+    tensors = helpers.read_tensors(folder)
+    ref = {rid: pp.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+    for steps in (helpers.trace_whole(reqs), helpers.trace_chunks(reqs)):
+        runner = _runner(folder, dtype, 64, helpers.trace_max_tokens(steps, 64))
+        _check(helpers.run_trace_with_runner(runner, steps), ref, TOL[dtype])
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    cases = dict(px.CASES)
+    cases["E"] = (px.PX_E, [3, 130, 64, 200, 65, 17], 64)
+    for name, (cfg, lengths, page) in cases.items():
+        for sharp in (False, True):
+            folder = px.write_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=21, sharp=sharp, ranks=px.RANKS[name])
+            reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab"], 300 + i) for i, n in enumerate(lengths)}
+            tensors = helpers.read_tensors(folder)
+            ref = {rid: pp.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
+            out[(name, sharp)] = (folder, cfg, reqs, ref, page)
+    return out
+
+
+def _steps(mode, reqs):
+    return {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_decode_tail(r, 32),
+            "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=5)}[mode](reqs)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
+@pytest.mark.parametrize("dtype,sharp", [("float32", True), ("bfloat16", False)])
+def test_modes_match_plain(models, name, mode, dtype, sharp):
+    """Whole prompts, most of a prompt then token by token, portions of 2 to 11 tokens, and mixed batches of up to four
+    unequal requests with pools so small that pages and state slots are used again."""
+    from kungfu_b200 import ops
+    folder, cfg, reqs, ref, page = models[(name, sharp)]
+    steps = _steps(mode, reqs)
+    runner = _runner(folder, dtype, page, helpers.trace_max_tokens(steps, page))
+    got = helpers.run_trace_with_runner(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _check(got, ref, TOL[dtype])
+    ops.raise_on_device_error(torch.device(DEV))
+    assert runner.cache.n_live == 0
+    if mode == "mixed":
+        assert all(n > g.pool.n_pages for n, g in zip(runner.cache.pages_handed_out(), runner.cache.groups))
+
+
+@pytest.mark.parametrize("name,page", [("A", 4), ("E", 64)])
+def test_batch_of_unequal_requests_equals_each_alone(models, name, page):
+    """32-bit: the logits of a request must not depend on what else is in its step."""
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, reqs, ref, _ = models[(name, True)]
+    runner = _runner(folder, "float32", page, 1024, graphs=False)
+    alone = {}
+    for rid, toks in reqs.items():
+        runner.cache.add_request(rid)
+        alone[rid] = runner.step([StepEntry(rid, toks, [len(toks) - 1])])[0].clone()
+        runner.cache.release(rid)
+    some = list(reqs)[:4]
+    for rid in some:
+        runner.cache.add_request(rid)
+    together = runner.step([StepEntry(rid, reqs[rid], [len(reqs[rid]) - 1]) for rid in some]).clone()
+    for i, rid in enumerate(some):
+        scale = float(ref[rid].abs().max())
+        assert float((together[i] - alone[rid]).abs().max()) / scale < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_long_decoding_from_captured_graphs(models, name, dtype):
+    """A short prompt and then 150 tokens one by one (the decode steps replay from a CUDA graph after the second)."""
+    folder, cfg, _, _, page = models[(name, dtype == "float32")]
+    toks = helpers.random_tokens(160, cfg["vocab"], 9)
+    ref = {"a": pp.forward(cfg, helpers.read_tensors(folder), toks).float()}
+    steps = helpers.trace_decode_tail({"a": toks}, 150)
+    runner = _runner(folder, dtype, page, 192)
+    got = helpers.run_trace_with_runner(runner, steps)
+    _check(got, ref, TOL[dtype])
+    assert any(s.get("graph") is not None for s in runner._graphs.values())
+
+
+def test_far_keys_and_old_state_carry_the_result(models):
+    """Keys hundreds of tokens back, across page borders, in a prompt and in decoding; and the books of this test: with
+    the sharp draw, losing one far page of the latent cache or one request's recurrent state moves the logits by far more
+    than the tolerance, so a fault there would show."""
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, _, _, page = models[("E", True)]
+    toks = helpers.random_tokens(600, cfg["vocab"], 77)
+    ref = pp.forward(cfg, helpers.read_tensors(folder), toks).float()
+    scale = float(ref.abs().max())
+    runner = _runner(folder, "float32", page, 1024, graphs=False)
+    runner.cache.add_request("a")
+    want = [0, 1, 2, 3, 62, 63, 64, 65, 127, 128, 129, 300, 447, 448, 449, 575]
+    got = runner.step([StepEntry("a", toks[:576], want)]).cpu()
+    for k, p in enumerate(want):
+        assert float((got[k] - ref[p]).abs().max()) / scale < TOL["float32"], p
+    for p in range(576, 590):
+        row = runner.step([StepEntry("a", [toks[p]], [0])])[0].cpu()
+        assert float((row - ref[p]).abs().max()) / scale < TOL["float32"], p
+    latent = runner.cache.storage[0]                               # layer 0: pages of the latent
+    table = runner.cache.block_table(0, "a")
+    saved = latent[table[0]].clone()
+    latent[table[0]].zero_()
+    row = runner.step([StepEntry("a", [toks[590]], [0])])[0].cpu()
+    assert float((row - ref[590]).abs().max()) / scale > 20 * TOL["float32"]
+    latent[table[0]] = saved
+    memory = runner.cache.storage[1][0]                            # layer 1: the delta rule's state
+    memory[runner.cache.state_slot("a")].zero_()
+    row = runner.step([StepEntry("a", [toks[591]], [0])])[0].cpu()
+    assert float((row - ref[591]).abs().max()) / scale > 20 * TOL["float32"]
+
+
+def test_a_state_slot_that_is_used_again_starts_from_zero(models):
+    from kungfu_b200.engine import StepEntry
+    folder, cfg, reqs, ref, page = models[("B", True)]
+    runner = _runner(folder, "float32", page, 128, max_requests=1, graphs=False)
+    for rid in ("r3", "r2", "r3"):
+        toks = reqs[rid]
+        runner.cache.add_request(rid)
+        assert runner.cache.state_slot(rid) == 0
+        a = runner.step([StepEntry(rid, toks[:2], [1])]).cpu()
+        b = runner.step([StepEntry(rid, toks[2:], [len(toks) - 3])]).cpu()
+        runner.cache.release(rid)
+        scale = float(ref[rid].abs().max())
+        assert float((a[0] - ref[rid][1]).abs().max()) / scale < TOL["float32"]
+        assert float((b[0] - ref[rid][len(toks) - 1]).abs().max()) / scale < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generate_through_the_entry_point(models, dtype):
+    """Greedy generation through Engine (scheduler, portions under a token budget, tokens drawn on the device, graphs)
+    against the plain implementation's best token at every place, near ties aside."""
+    import kungfu_b200
+    from kungfu_b200.sampling import Sampling
+    folder, cfg, reqs, _, page = models[("E", False)]
+    tensors = helpers.read_tensors(folder)
+    eng = kungfu_b200.Engine(folder, dtype=dtype, device=DEV, ctx=512, batch=64, parallel=4, page_size=page,
+                             max_tokens_in_cache=1024)
+    prompts = [reqs["r1"], reqs["r0"], reqs["r3"], reqs["r5"], reqs["r2"]]
+    outs = eng.generate(prompts, Sampling(temperature=0.0), max_tokens=12, ignore_eos=True)
+    margin = 1e-3 if dtype == "float32" else 5e-2
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        seq = list(p)
+        for tok in o:
+            logits = pp.forward(cfg, tensors, seq)[-1]
+            top = torch.topk(logits, 2).values
+            if float(top[0] - top[1]) > margin * float(logits.abs().max()):
+                assert int(torch.argmax(logits)) == tok
+            seq.append(tok)
+
+
+def test_programs_in_bin(models, tmp_path):
+    """bin/trace_run replays a trace of a Petanex folder; bin/kungfu inspects the folder and completes a prompt."""
+    folder, cfg, reqs, ref, page = models[("A", True)]
+    steps = helpers.trace_mixed(reqs, seed=2)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", str(helpers.trace_max_tokens(steps, 64))],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    at = {rid: 0 for rid in reqs}
+    scale = max(float(r.abs().max()) for r in ref.values())
+    for s in steps:
+        rows = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        k = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                assert float(np.abs(rows[k] - ref[e["id"]][at[e["id"]] + w].numpy()).max()) / scale < TOL["float32"]
+                k += 1
+            at[e["id"]] += len(e["tokens"])
+    kungfu = os.path.join(ROOT, "bin", "kungfu")
+    p = subprocess.run([sys.executable, kungfu, "inspect", folder, "--json"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    doc = json.loads(p.stdout)
+    assert doc["architecture"] == "Petanex" and doc["layers"] == 4 and not doc["missing"] and not doc["unexpected"]
+    assert [s["kind"] for s in doc["states"]] == ["recurrent+conv_tail", "latent_cache"] * 2
+    p = subprocess.run([sys.executable, kungfu, "generate", "--model", folder, "--ids", json.dumps(reqs["r1"]), "--max-tokens", "5",
+                        "--dtype", "float32", "--ignore-eos", "--ctx", "256"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    gen = json.loads(p.stdout.strip().splitlines()[-1])["generated"]
+    tensors = helpers.read_tensors(folder)
+    seq = list(reqs["r1"])
+    for tok in gen:
+        logits = pp.forward(cfg, tensors, seq)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) > 1e-3 * float(logits.abs().max()):
+            assert int(torch.argmax(logits)) == tok
+        seq.append(tok)
