@@ -63,6 +63,8 @@ def cmd_inspect(args) -> int:
         return 1
     arch = registry.find(cfg.architecture)
     tensors = open_model_tensors(args.model)
+    if hasattr(cfg, "with_shapes"):                         # sizes that only a tensor's shape gives
+        cfg = cfg.with_shapes(lambda n: tuple(tensors[n][1].shape) if n in tensors else None)
     specs = {s.name: s for s in arch.tensor_specs(cfg)}
     missing = sorted(n for n in specs if n not in tensors)
     unexpected = sorted(n for n in tensors if n not in specs)
@@ -297,7 +299,7 @@ def cmd_random_weights(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="kungfu", description="Gemma 2 and Bolonex on B200: inspect, describe, generate, score, bench")
+    ap = argparse.ArgumentParser(prog="kungfu", description="Gemma 2, Bolonex and Petanex on B200: inspect, describe, generate, score, bench")
     sub = ap.add_subparsers(dest="cmd", required=True)
     p = sub.add_parser("inspect", help="what the folder is, how its tensors group, what state each layer keeps")
     p.add_argument("model")

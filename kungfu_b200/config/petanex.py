@@ -217,6 +217,20 @@ class PetanexConfig:
             out["token_side"] = {"dim": self.side_dim}
         return out
 
+    def with_shapes(self, shape_of) -> "PetanexConfig":
+        """This configuration with the sizes that only tensors give filled in: `shape_of(name)` is a stored tensor's shape
+        or None.  The ranks of a channel_delta layer's factored decay and gate are the row counts of `l<i>.mix.a1` and
+        `l<i>.mix.g1`."""
+        layers = []
+        for i, l in enumerate(self.layers):
+            if l.type == CHANNEL_DELTA:
+                a, g = shape_of(f"l{i}.mix.a1"), shape_of(f"l{i}.mix.g1")
+                m = dataclasses.replace(l.mixer, decay_rank=l.mixer.decay_rank if l.mixer.decay_rank is not None else (int(a[0]) if a else None),
+                                        gate_rank=l.mixer.gate_rank if l.mixer.gate_rank is not None else (int(g[0]) if g else None))
+                l = dataclasses.replace(l, mixer=m)
+            layers.append(l)
+        return dataclasses.replace(self, layers=tuple(layers))
+
     def replace(self, **kw) -> "PetanexConfig":
         cfg = dataclasses.replace(self, **kw)
         cfg.validate()

@@ -25,14 +25,10 @@ MATRIX_STD = 0.02
 CONV_STD = 0.3
 
 
-def _ranks(m, shape_of=None, p: str = "") -> tuple:
-    """(decay rank, gate rank) of a channel_delta mixer: the file's keys, else the stored tensors' shapes, else a default."""
-    def one(key_value, name):
-        if key_value is not None:
-            return key_value
-        shape = shape_of(name) if shape_of is not None else None
-        return int(shape[0]) if shape else DEFAULT_RANK
-    return one(m.decay_rank, p + "mix.a1"), one(m.gate_rank, p + "mix.g1")
+def _ranks(m) -> tuple:
+    """(decay rank, gate rank) of a channel_delta mixer: the file's keys or the stored tensors' shapes
+    (`PetanexConfig.with_shapes`), else a default (random weights)."""
+    return (m.decay_rank if m.decay_rank is not None else DEFAULT_RANK, m.gate_rank if m.gate_rank is not None else DEFAULT_RANK)
 
 
 def _expert_specs(p: str, ff: int, W: int) -> list[TensorSpec]:
@@ -117,7 +113,7 @@ def _mixer(cfg: PetanexConfig, w: WeightStore, i: int):
     names = [f"{p}mix.{n}" for n, _ in rows] + [p + "mix.b"]
     a2 = g2 = None
     if l.type == CHANNEL_DELTA:
-        ra, rg = _ranks(m, w.shape_of, p)
+        ra, rg = _ranks(m)
         mats += [w.take(p + "mix.a1", (ra, W)), w.take(p + "mix.g1", (rg, W))]
         names += [p + "mix.a1", p + "mix.g1"]
         a2, g2 = w.take(p + "mix.a2", (m.heads * m.dim, ra)), w.take(p + "mix.g2", (m.heads * m.vdim, rg))
@@ -167,6 +163,7 @@ def _feed_forward(cfg: PetanexConfig, w: WeightStore, i: int):
 
 
 def build(cfg: PetanexConfig, w: WeightStore) -> DecoderModel:
+    cfg = cfg.with_shapes(w.shape_of)
     W, L = cfg.width, len(cfg.layers)
     table = w.take("embed", (cfg.vocab, W))
     side_table = w.take("side.embed", (cfg.vocab, L * cfg.side_dim)) if cfg.side_dim else None
