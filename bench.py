@@ -7,8 +7,9 @@
                     (kernels alone, JSON lines; for the summaries in profiles/)
     python bench.py --compare bolonex
     python bench.py --compare petanex
-                    (Bolonex beside Gemma 2 at equal layer sizes: prefill and decode throughput and, per operation, the
-                    time of one step against the time its bytes take at the measured copy rate; one JSON line)
+                    (Bolonex beside Gemma 2, or Petanex beside Bolonex, at equal layer sizes: prefill and decode throughput
+                    and, per operation, the time of one step against the time its bytes, or its multiply-adds, take at the
+                    measured rates; one JSON line)
 
 A "step" is one decode step: every live request gets one token.  Default: the layer sizes of Gemma 2 2B, random
 bfloat16 weights, 8 requests at a context of 8192 tokens.  `value` is decoded tokens per second timed with CUDA events

@@ -10,14 +10,18 @@
 // holds of it (one token, a portion, a whole prompt), and the state is carried exactly: a token's result does not depend
 // on how the sequence was cut.
 //
-// Work split: a block of 128 threads owns (request, head, 128 / LANES value columns).  Thread (c, l) keeps rows
+// Two kernels.  What does not depend on the state (the unit vectors, the sigmoid, the decays: the transcendental work)
+// is computed once per (row, head), side by side over the whole step, and left laid out as the walk stages it.
+// The walk: a block of 128 threads owns (request, head, 128 / LANES value columns).  Thread (c, l) keeps rows
 // l*NR .. l*NR+NR-1 of column c in registers (d <= LANES * NR; rows beyond d are zero and stay zero); the LANES lanes of
-// a column add their partial dot products by shuffles, each from two interleaved partial sums so that a chain of
-// dependent multiply-adds is NR / 2 long.  Rows of q, k, the decays, v and beta of R tokens at a time arrive in shared
-// memory by cp.async into one of two stages while the stage before is walked; there the unit norms, the sigmoid and
-// the decays (the transcendental work) are done by all threads side by side, so that the serial walk is multiply-adds
-// and shared loads only.  A lane's chunk of a staged row starts every NR + 4 floats: the lanes of a column then read
-// different banks with 16-byte loads.
+// a column add their shares of S^T k by shuffles (the one reduction on the chain from token to token), each from two
+// interleaved partial sums so that a chain of dependent multiply-adds is NR / 2 long; their shares of S^T q go to shared
+// memory and are summed, in a fixed order, after the walk over the stage.  Rows of R tokens at a time arrive in shared
+// memory by 16-byte cp.async copies into one of two stages while the stage before is walked, so that the serial walk is
+// multiply-adds and shared loads only.  A lane's chunk of a staged row starts every LS floats (NR + 4; NR where that is
+// 4): the lanes of a column then read different banks with 16-byte loads.  With one long prompt in a step the walk
+// has heads x d x dv / NR threads and no more, so NR is small: what limits it is the latency of a warp's chain, which
+// only more warps per scheduler hide.
 //
 // kf_head_norm_gate follows: every head's o is divided by its root mean square over dv, times a weight vector shared
 // by the heads, times silu or sigmoid of a gate column.
@@ -41,29 +45,76 @@ __device__ __forceinline__ float kf_softplus(float z) { return z > 20.f ? z : lo
 __device__ __forceinline__ void kf_cp_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void kf_cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 
-// NR rows of a column per thread, LANES threads per column (d <= NR * LANES), 128 / LANES columns per block.
-template <typename TW, int NR, int LANES>
-__global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
+// Everything of a token that does not depend on the state, once per (row, head) and side by side over the whole step:
+// the unit vectors q (times d^-1/2) and k, the decays (per key channel, or one) and beta.  q, k and the decays are
+// written as the walk wants them in shared memory (a lane's chunk of NR numbers every LS floats; any floats
+// between chunks are never read), so that a stage of the walk is filled by 16-byte copies:
+//   prep[((row * H + h) * 3 + {0: q, 1: k, 2: decays}) * ROW + (i / NR) * LS + i % NR],   small[(row * H + h) * 2 + {0: beta, 1: decay}]
+template <typename TW>
+__global__ void __launch_bounds__(128) delta_prepare_kernel(KfDeltaArgs p, float* __restrict__ prep, float* __restrict__ small,
+                                                            int T, int NR, int LANES) {
   kf_pdl_trigger();
   kf_pdl_wait();
-  constexpr int CB = 128 / LANES;                // value columns of a block
-  constexpr int R = LANES >= 16 ? 4 : 8;         // tokens staged at a time
-  constexpr int LS = NR + 4;                     // floats between the chunks of two lanes
+  const int lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long)T * p.H) return;
+  const int t = (int)(item / p.H), h = (int)(item - (long)t * p.H);
+  const int kh = h / (p.H / p.KH), d = p.d, LS = NR == 4 ? 4 : NR + 4, ROW = LANES * LS, DP = NR * LANES;
+  const float* qs = p.qkv + (size_t)t * p.ld_qkv + p.q0 + kh * d;
+  const float* ks = p.qkv + (size_t)t * p.ld_qkv + p.k0 + kh * d;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    sq = fmaf(qs[i], qs[i], sq);
+    sk = fmaf(ks[i], ks[i], sk);
+  }
+  sq = kf_warp_sum(sq);
+  sk = kf_warp_sum(sk);
+  const float fq = 1.f / sqrtf((float)d) / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
+  const float rate = expf(kf_load((const TW*)p.a_log, h));
+  float* dst = prep + (size_t)item * 3 * ROW;
+  for (int i = lane; i < DP; i += 32) {
+    const int at = (i / NR) * LS + (i % NR);
+    const bool in = i < d;
+    dst[at] = in ? qs[i] * fq : 0.f;
+    dst[ROW + at] = in ? ks[i] * fk : 0.f;
+    if (p.per_channel) {
+      float g = 1.f;
+      if (in) g = expf(-rate * kf_softplus(p.decay[(size_t)t * p.ld_decay + p.decay0 + h * d + i] + kf_load((const TW*)p.dt_bias, h * d + i)));
+      dst[2 * ROW + at] = g;
+    }
+  }
+  if (lane == 0) {
+    small[item * 2] = 1.f / (1.f + expf(-p.beta[(size_t)t * p.ld_beta + p.beta0 + h]));
+    if (!p.per_channel)
+      small[item * 2 + 1] = expf(-rate * kf_softplus(p.decay[(size_t)t * p.ld_decay + p.decay0 + h] + kf_load((const TW*)p.dt_bias, h)));
+  }
+}
+
+// The walk.  NR rows of a column per thread, LANES threads per column (d <= NR * LANES), THREADS / LANES columns per block.
+template <int NR, int LANES, int THREADS>
+__global__ void __launch_bounds__(THREADS) delta_rule_kernel(KfDeltaArgs p, const float* __restrict__ prep, const float* __restrict__ small) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  constexpr int CB = THREADS / LANES;            // value columns of a block
+  constexpr int LS = NR == 4 ? 4 : NR + 4;       // floats between the chunks of two lanes (16-byte loads of the lanes of a
+                                                 // quarter warp then fall into different banks)
   constexpr int ROW = LANES * LS;
-  constexpr int DP = LANES * NR;                 // rows of S the block's threads hold (rows beyond d stay zero)
+  constexpr int R = ROW > 200 ? 4 : 8;           // tokens staged at a time
   __shared__ __align__(16) float q_s[2][R][ROW];
   __shared__ __align__(16) float k_s[2][R][ROW];
   __shared__ __align__(16) float g_s[2][R][ROW];
-  __shared__ float bias_s[ROW];
   __shared__ float v_s[2][R][CB];
-  __shared__ float beta_s[2][R], g1_s[2][R];
+  __shared__ float small_s[2][R][2];
+  __shared__ float o_part[2][R][CB][LANES + 1];  // every lane's share of o: summed over the lanes after the walk
   const int req = blockIdx.x / p.H, h = blockIdx.x - req * p.H;
   const int n = p.req_n_rows[req];
   if (n <= 0) return;
   const int row0 = p.req_row_start[req], slot = p.req_state_slot[req];
-  const int kh = h / (p.H / p.KH);
-  const int tid = threadIdx.x, c = tid / LANES, l = tid % LANES, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, c = tid / LANES, l = tid % LANES;
   const int col0 = blockIdx.y * CB, col = col0 + c;
   const bool col_ok = col < p.dv;
   const int d = p.d, dv = p.dv;
@@ -74,39 +125,35 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
     const int r = l * NR + i;
     S[i] = (r < d && col_ok) ? sp[(size_t)r * dv + col] : 0.f;
   }
-  const float rate = expf(kf_load((const TW*)p.a_log, h));
-  const float q_scale = 1.f / sqrtf((float)d);
-  const float bias_h = p.per_channel ? 0.f : kf_load((const TW*)p.dt_bias, h);
-  if (p.per_channel)
-    for (int i = tid; i < DP; i += 128) bias_s[(i / NR) * LS + (i % NR)] = i < d ? kf_load((const TW*)p.dt_bias, h * d + i) : 0.f;
 
-  // rows t0 .. t0 + nr - 1 of the request, as they stand in global memory, into stage `buf` (asynchronous copies)
+  // rows t0 .. t0 + nr - 1 of the request into stage `buf` (asynchronous copies, 16 bytes where the source allows)
   auto issue = [&](int buf, int t0, int nr) {
-    for (int idx = tid; idx < nr * DP; idx += 128) {
-      const int tt = idx / DP, i = idx - tt * DP;
-      const int at = (i / NR) * LS + (i % NR);
-      const size_t row = (size_t)(row0 + t0 + tt);
-      if (i < d) {
-        kf_cp_async4(&q_s[buf][tt][at], p.qkv + row * p.ld_qkv + p.q0 + kh * d + i);
-        kf_cp_async4(&k_s[buf][tt][at], p.qkv + row * p.ld_qkv + p.k0 + kh * d + i);
-        if (p.per_channel) kf_cp_async4(&g_s[buf][tt][at], p.decay + row * p.ld_decay + p.decay0 + h * d + i);
-      } else {
-        q_s[buf][tt][at] = 0.f;
-        k_s[buf][tt][at] = 0.f;
-        g_s[buf][tt][at] = 1e30f;                // a raw decay that gives exp(-rate * 1e30) = 0; the rows it scales are zero
-      }
+    constexpr int V4 = ROW / 4;
+    for (int idx = tid; idx < nr * V4; idx += THREADS) {
+      const int tt = idx / V4, j = idx - tt * V4;
+      const float* src = prep + ((size_t)(row0 + t0 + tt) * p.H + h) * 3 * ROW + j * 4;
+      kf_cp_async16(&q_s[buf][tt][j * 4], src);
+      kf_cp_async16(&k_s[buf][tt][j * 4], src + ROW);
+      if (p.per_channel) kf_cp_async16(&g_s[buf][tt][j * 4], src + 2 * ROW);
     }
-    for (int idx = tid; idx < nr * CB; idx += 128) {
+    for (int idx = tid; idx < nr * CB; idx += THREADS) {
       const int tt = idx / CB, cc = idx - tt * CB;
       if (col0 + cc < dv) kf_cp_async4(&v_s[buf][tt][cc], p.qkv + (size_t)(row0 + t0 + tt) * p.ld_qkv + p.v0 + h * dv + col0 + cc);
       else v_s[buf][tt][cc] = 0.f;
     }
-    if (tid < nr) {
-      const size_t row = (size_t)(row0 + t0 + tid);
-      kf_cp_async4(&beta_s[buf][tid], p.beta + row * p.ld_beta + p.beta0 + h);
-      if (!p.per_channel) kf_cp_async4(&g1_s[buf][tid], p.decay + row * p.ld_decay + p.decay0 + h);
-    }
+    if (tid < nr * 2) kf_cp_async4(&small_s[buf][tid >> 1][tid & 1], small + ((size_t)(row0 + t0 + (tid >> 1)) * p.H + h) * 2 + (tid & 1));
     asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // o of the rows t0 .. t0 + nr - 1, whose lanes' shares stand in o_part[buf]: lane sums in a fixed order, then the store
+  auto finish = [&](int buf, int t0, int nr) {
+    for (int idx = tid; idx < nr * CB; idx += THREADS) {
+      const int tt = idx / CB, cc = idx - tt * CB;
+      if (col0 + cc >= dv) continue;
+      float o = 0.f;
+#pragma unroll
+      for (int j = 0; j < LANES; ++j) o += o_part[buf][tt][cc][j];
+      p.out[(size_t)(row0 + t0 + tt) * p.ld_out + h * dv + col0 + cc] = o;
+    }
   };
 
   const int n_chunks = (n + R - 1) / R;
@@ -116,29 +163,8 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                             // this stage has landed; the walk over the stage before is over
     if (ch + 1 < n_chunks) issue(buf ^ 1, t0 + R, min(R, n - t0 - R));
-    // unit vectors, decays and beta of the staged rows, by all threads side by side: one warp per token
-    for (int tt = warp; tt < nr; tt += 4) {
-      float sq = 0.f, sk = 0.f;
-      for (int i = lane; i < DP; i += 32) {
-        const int at = (i / NR) * LS + (i % NR);
-        sq = fmaf(q_s[buf][tt][at], q_s[buf][tt][at], sq);
-        sk = fmaf(k_s[buf][tt][at], k_s[buf][tt][at], sk);
-      }
-      sq = kf_warp_sum(sq);
-      sk = kf_warp_sum(sk);
-      const float fq = q_scale / sqrtf(sq + 1e-6f), fk = 1.f / sqrtf(sk + 1e-6f);
-      for (int i = lane; i < DP; i += 32) {
-        const int at = (i / NR) * LS + (i % NR);
-        q_s[buf][tt][at] *= fq;
-        k_s[buf][tt][at] *= fk;
-        if (p.per_channel) g_s[buf][tt][at] = expf(-rate * kf_softplus(g_s[buf][tt][at] + bias_s[at]));
-      }
-      if (lane == 0) {
-        beta_s[buf][tt] = 1.f / (1.f + expf(-beta_s[buf][tt]));
-        if (!p.per_channel) g1_s[buf][tt] = expf(-rate * kf_softplus(g1_s[buf][tt] + bias_h));
-      }
-    }
-    __syncthreads();
+    if (ch > 0) finish(buf ^ 1, t0 - R, R);
+#pragma unroll 2
     for (int tt = 0; tt < nr; ++tt) {              // the walk
       const float* kq = &k_s[buf][tt][l * LS];
       const float* qq = &q_s[buf][tt][l * LS];
@@ -155,7 +181,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
           kva = fmaf(S[i], k4.x, kva); kvb = fmaf(S[i + 1], k4.y, kvb); kva = fmaf(S[i + 2], k4.z, kva); kvb = fmaf(S[i + 3], k4.w, kvb);
         }
       } else {
-        const float g = g1_s[buf][tt];
+        const float g = small_s[buf][tt][1];
 #pragma unroll
         for (int i = 0; i < NR; i += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
@@ -167,7 +193,7 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
       float kv = kva + kvb;
 #pragma unroll
       for (int o = 1; o < LANES; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
-      const float u = beta_s[buf][tt] * (v_s[buf][tt][c] - kv);
+      const float u = small_s[buf][tt][0] * (v_s[buf][tt][c] - kv);
       float oa = 0.f, ob = 0.f;
 #pragma unroll
       for (int i = 0; i < NR; i += 4) {
@@ -176,12 +202,11 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
         S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
         oa = fmaf(S[i], q4.x, oa); ob = fmaf(S[i + 1], q4.y, ob); oa = fmaf(S[i + 2], q4.z, oa); ob = fmaf(S[i + 3], q4.w, ob);
       }
-      float o = oa + ob;
-#pragma unroll
-      for (int sh = 1; sh < LANES; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
-      if (l == 0 && col_ok) p.out[(size_t)(row0 + t0 + tt) * p.ld_out + h * dv + col] = o;
+      o_part[buf][tt][c][l] = oa + ob;            // off the chain from token to token: summed by `finish`
     }
   }
+  __syncthreads();
+  finish((n_chunks - 1) & 1, (n_chunks - 1) * R, n - (n_chunks - 1) * R);
   if (p.writes) {
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
@@ -191,27 +216,48 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(KfDeltaArgs p) {
   }
 }
 
-// d up to 256 key channels, any dv.  Rows of single-token steps and of prompt portions run the same kernel.
+// Rows per thread, lanes per column and threads per block by key size: few rows per thread, because one long prompt has
+// heads x d x dv / NR threads and no more, and only several warps per scheduler hide the latency of a warp's chain.
+static void delta_shape(int d, int* nr, int* lanes, int* threads) {
+  // (measured at 16 heads x 128 x 128, one prompt of 2,048 tokens: 8 rows x 16 lanes 666 us; 4 rows x 32 lanes in blocks of
+  // 256 threads 771 us, its fifth shuffle step costing more than the second warp per scheduler hides; 16 rows x 8 lanes 1,010 us)
+  if (d <= 32) { *nr = 8; *lanes = 4; *threads = 128; }
+  else if (d <= 64) { *nr = 8; *lanes = 8; *threads = 128; }
+  else if (d <= 128) { *nr = 8; *lanes = 16; *threads = 128; }
+  else { *nr = 16; *lanes = 16; *threads = 128; }
+}
+
+// Floats of scratch the walk wants per (row, head): three staged rows.
+KF_API int kf_delta_rule_row_floats(int d) {
+  int nr, lanes, threads;
+  delta_shape(d, &nr, &lanes, &threads);
+  return 3 * lanes * (nr == 4 ? 4 : nr + 4);
+}
+
+// d up to 256 key channels, any dv.  Rows of single-token steps and of prompt portions run the same two kernels.
+// prep: T * H * kf_delta_rule_row_floats(d) floats (16-byte aligned); small: T * H * 2 floats.
 KF_API int kf_delta_rule(const float* qkv, int ld_qkv, int q0, int k0, int v0, const float* beta, int ld_beta, int beta0,
                          const float* decay, int ld_decay, int decay0, int per_channel, const void* dt_bias, const void* a_log,
                          int w_dtype, float* state, float* out, int ld_out, int H, int KH, int d, int dv, int n_reqs,
-                         const int* req_row_start, const int* req_n_rows, const int* req_state_slot, int writes,
-                         cudaStream_t stream) {
-  if (n_reqs <= 0) return KF_OK;
+                         const int* req_row_start, const int* req_n_rows, const int* req_state_slot, int writes, int T,
+                         float* prep, float* small, cudaStream_t stream) {
+  if (n_reqs <= 0 || T <= 0) return KF_OK;
   if (d < 1 || d > 256 || dv < 1 || H < 1 || KH < 1 || H % KH) return KF_ERR_SIZE;
+  if (!prep || !small || ((uintptr_t)prep & 15)) return KF_ERR_ALIGN;
   KfDeltaArgs p{qkv, ld_qkv, q0, k0, v0, beta, ld_beta, beta0, decay, ld_decay, decay0, per_channel, dt_bias, a_log,
                 state, out, ld_out, H, KH, d, dv, n_reqs, req_row_start, req_n_rows, req_state_slot, writes};
-#define KF_GO(TW)                                                                                                        \
-  do {                                                                                                                   \
-    if (d <= 32) kf_launch(delta_rule_kernel<TW, 8, 4>, dim3(n_reqs * H, kf_ceil_div(dv, 32)), dim3(128), 0, stream, p);       \
-    else if (d <= 64) kf_launch(delta_rule_kernel<TW, 16, 4>, dim3(n_reqs * H, kf_ceil_div(dv, 32)), dim3(128), 0, stream, p); \
-    else if (d <= 128) kf_launch(delta_rule_kernel<TW, 16, 8>, dim3(n_reqs * H, kf_ceil_div(dv, 16)), dim3(128), 0, stream, p); \
-    else kf_launch(delta_rule_kernel<TW, 16, 16>, dim3(n_reqs * H, kf_ceil_div(dv, 8)), dim3(128), 0, stream, p);             \
-  } while (0)
-  if (w_dtype == KF_F32) KF_GO(float);
-  else if (w_dtype == KF_BF16) KF_GO(__nv_bfloat16);
+  int nr, lanes, threads;
+  delta_shape(d, &nr, &lanes, &threads);
+  const dim3 pgrid(kf_ceil_div((long)T * H, 4));
+  if (w_dtype == KF_F32) kf_launch(delta_prepare_kernel<float>, pgrid, dim3(128), 0, stream, p, prep, small, T, nr, lanes);
+  else if (w_dtype == KF_BF16) kf_launch(delta_prepare_kernel<__nv_bfloat16>, pgrid, dim3(128), 0, stream, p, prep, small, T, nr, lanes);
   else return KF_ERR_DTYPE;
-#undef KF_GO
+  KF_CHECK_LAUNCH();
+  const dim3 grid(n_reqs * H, kf_ceil_div(dv, threads / lanes));
+  if (d <= 32) kf_launch(delta_rule_kernel<8, 4, 128>, grid, dim3(128), 0, stream, p, (const float*)prep, (const float*)small);
+  else if (d <= 64) kf_launch(delta_rule_kernel<8, 8, 128>, grid, dim3(128), 0, stream, p, (const float*)prep, (const float*)small);
+  else if (d <= 128) kf_launch(delta_rule_kernel<8, 16, 128>, grid, dim3(128), 0, stream, p, (const float*)prep, (const float*)small);
+  else kf_launch(delta_rule_kernel<16, 16, 128>, grid, dim3(128), 0, stream, p, (const float*)prep, (const float*)small);
   KF_CHECK_LAUNCH();
   return KF_OK;
 }

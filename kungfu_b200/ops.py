@@ -680,11 +680,17 @@ def delta_rule(qkv, q0: int, k0: int, v0: int, beta, beta0: int, decay, decay0: 
     o = S^T q.  q, k, v are column ranges of `qkv` (32-bit, after convolution and activation), made unit vectors per head
     here (q also times dim^-1/2); beta = sigmoid(beta[:, beta0 + h]); g = exp(-exp(a_log[h]) softplus(decay[:, decay0 + ...] +
     dt_bias)).  Query/key head of head h: h // (heads // kv_heads).  out: 32-bit [rows, heads * vdim]."""
-    _check(library().kf_delta_rule(_p(qkv), qkv.shape[1], int(q0), int(k0), int(v0), _p(beta), beta.shape[1], int(beta0),
-                                   _p(decay), decay.shape[1], int(decay0), int(bool(per_channel)), _p(dt_bias), _p(a_log),
-                                   _dt(a_log), _p(state), _p(out), out.shape[1], heads, kv_heads, dim, vdim, ctx.n_reqs,
-                                   _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), _stream()),
-           "delta_rule")
+    T = out.shape[0]
+    lib = library()
+    # what does not depend on the state (unit vectors, decays, beta) is computed for all rows first, into scratch
+    prep = ctx.buf("delta_prep", (T * heads * lib.kf_delta_rule_row_floats(int(dim)),), torch.float32)
+    small = ctx.buf("delta_small", (T * heads * 2,), torch.float32)
+    _check(lib.kf_delta_rule(_p(qkv), qkv.shape[1], int(q0), int(k0), int(v0), _p(beta), beta.shape[1], int(beta0),
+                             _p(decay), decay.shape[1], int(decay0), int(bool(per_channel)), _p(dt_bias), _p(a_log),
+                             _dt(a_log), _p(state), _p(out), out.shape[1], heads, kv_heads, dim, vdim, ctx.n_reqs,
+                             _p(ctx.req_row_start), _p(ctx.req_n_rows), _p(ctx.req_state_slot), int(writes), T, _p(prep),
+                             _p(small), _stream()), "delta_rule")
+    add_launches(1)
 
 
 _GATE_ACT = {"silu": 0, "sigmoid": 1}
