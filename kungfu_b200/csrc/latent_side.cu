@@ -7,7 +7,26 @@
 //                        same pass, and optionally a plain copy of the new x[t] in another element type.
 // kf_side_gate:          out[t, j] = gelu_tanh(gate[t, j]) * table[token[t], col0 + j]: the gate of a per-token input whose
 //                        second factor is looked up by token id.
+// kf_repeat_rows:        out[t * parts + j] = in[t] for two integer arrays at once: the positions and requests of a step
+//                        whose every row is presented to the attention kernels as `parts` rows of fewer heads.
 #include "common.cuh"
+
+__global__ void repeat_rows_kernel(const int* __restrict__ a, const int* __restrict__ b, int* __restrict__ out_a,
+                                   int* __restrict__ out_b, int T, int parts) {
+  kf_pdl_trigger();
+  kf_pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * parts) return;
+  out_a[i] = a[i / parts];
+  out_b[i] = b[i / parts];
+}
+
+KF_API int kf_repeat_rows(const int* a, const int* b, int* out_a, int* out_b, int T, int parts, cudaStream_t stream) {
+  if (T <= 0 || parts <= 0) return KF_OK;
+  kf_launch(repeat_rows_kernel, dim3(kf_ceil_div((long)T * parts, 256)), dim3(256), 0, stream, a, b, out_a, out_b, T, parts);
+  KF_CHECK_LAUNCH();
+  return KF_OK;
+}
 
 template <typename TW, typename TC>
 __global__ void latent_append_kernel(const float* __restrict__ proj, int ld, int c0, int rank, const TW* __restrict__ w, float eps,

@@ -716,6 +716,14 @@ def latent_append(proj, c0: int, rank: int, weight, eps: float, ctx, cache) -> N
                                       _p(cache.pages), _dt(cache.pages), D, T, _stream()), "latent_append")
 
 
+@_dispatch("repeat_rows")
+def repeat_rows(a, b, parts: int, out_a, out_b) -> None:
+    """out_a[t * parts + j] = a[t], out_b likewise (int32): a step's positions and requests for rows that are presented
+    to a kernel as `parts` rows each."""
+    T = a.shape[0]
+    _check(library().kf_repeat_rows(_p(a), _p(b), _p(out_a), _p(out_b), T, int(parts), _stream()), "repeat_rows")
+
+
 def _grouped(x, x_off, ldx, x_gstride, row_index, row_div, w, w_gstride, out, o_off, ldo, o_gstride, tiles, max_tiles,
              n_groups, T, N, K, gated, limit, what):
     tg, tr, tn, nt = tiles if tiles is not None else (None, None, None, None)

@@ -29,6 +29,30 @@ def latent_head_size(rank: int) -> int:
     raise ValueError(f"a latent of {rank} elements is above {_KERNEL_HEAD_SIZES[-1]}, the largest head the attention kernels take")
 
 
+class _RowsAsParts:
+    """A decode step seen by the attention kernels as `parts` rows per token, each with 1 / parts of the heads: the same
+    pages and block tables, positions and requests repeated.  (The tensor-core decode kernel takes the query heads of
+    one key/value head as the rows of ONE 16-row tile; a latent has a single key/value head for all heads.)"""
+
+    def __init__(self, ctx, parts: int):
+        T = ctx.n_rows
+        self.positions = ctx.buf("latent_positions", (T * parts,), torch.int32)
+        self.row_req = ctx.buf("latent_row_req", (T * parts,), torch.int32)
+        ops.repeat_rows(ctx.positions, ctx.row_req, parts, self.positions, self.row_req)
+        self.block_tables, self.max_kv_len = ctx.block_tables, ctx.max_kv_len
+        self.n_rows = self.n_dec_rows = T * parts
+        self.n_pre_rows = self.n_tiles = self.n_wide = 0
+        self.dec_rows = self.pre_rows = None
+
+
+def _decode_parts(n_heads: int) -> int:
+    """Into how many parts the heads are cut for decode steps: the fewest that leave at most 16 heads each."""
+    for parts in range(1, n_heads + 1):
+        if n_heads % parts == 0 and n_heads // parts <= 16:
+            return parts
+    return 1
+
+
 class LatentAttention(Mixer):
     def __init__(self, w_q: torch.Tensor, w_dkv: torch.Tensor, c_norm: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor,
                  wo: torch.Tensor, *, n_heads: int, dim: int, vdim: int, rank: int, scale: float, norm_eps: float,
@@ -67,7 +91,12 @@ class LatentAttention(Mixer):
         q = ctx.buf("attn_q", (T, H * D), ctx.act_dtype)
         ops.head_linear(proj, 0, self.w_uk_t, q)
         o = ctx.buf("attn_o", (T, H * D), ctx.act_dtype)
-        ops.paged_attention(q, o, ctx, cache, H, 1, D, self.scale, 0.0, self.window)
+        parts = _decode_parts(H) if (H > 16 and getattr(ctx, "decode_only", False)) else 1
+        if parts > 1 and H // parts >= 4:
+            ops.paged_attention(q.view(T * parts, (H // parts) * D), o.view(T * parts, (H // parts) * D), _RowsAsParts(ctx, parts),
+                                cache, H // parts, 1, D, self.scale, 0.0, self.window)
+        else:
+            ops.paged_attention(q, o, ctx, cache, H, 1, D, self.scale, 0.0, self.window)
         v = ctx.buf("latent_v", (T, H * self.vdim), ctx.act_dtype)
         ops.head_linear(o, 0, self.w_uv, v)
         y = ctx.buf("branch_out", (T, self.width), torch.float32)

@@ -313,6 +313,10 @@ class CpuOps:
             cache.pages[page, 0, 0, pos % cache.page_size] = row.to(cache.pages.dtype)
             cache.pages[page, 1, 0, pos % cache.page_size] = row.to(cache.pages.dtype)
 
+    def repeat_rows(self, a, b, parts, out_a, out_b):
+        out_a.copy_(a.repeat_interleave(parts))
+        out_b.copy_(b.repeat_interleave(parts))
+
     def head_linear(self, x, col0, weight, out):
         H, O, I = weight.shape
         T = out.shape[0]
