@@ -62,8 +62,8 @@ PX_B = config(96, 257, [layer("latent_attention", latent(3, 24, 16, 40, 0.2), mo
                         layer("delta", delta(6, 6, 8, 8, 4), dense(64))], scale=0.5, eps=1e-6)
 
 # rows that are no multiple of 16 bytes (width 100), odd sizes everywhere, keys of 136 (the widest instance of the
-# recurrence), five taps, twenty heads over a latent (more than a tensor-core tile of query rows), three groups of four
-PX_C = config(100, 333, [layer("channel_delta", delta(2, 1, 136, 20, 5), moe(12, 4, 30, 2.0, 0.8, groups=(3, 1), shared=(30, 2.0))),
+# recurrence), five taps, twenty heads over a latent (more than a tensor-core tile of query rows), two of three groups of four
+PX_C = config(100, 333, [layer("channel_delta", delta(2, 1, 136, 20, 5), moe(12, 4, 30, 2.0, 0.8, groups=(3, 2), shared=(30, 2.0))),
                          layer("latent_attention", latent(20, 12, 10, 33, 0.25), dense(150)),
                          layer("delta", delta(6, 3, 12, 7, 2), dense(70))], scale=1.5, side=5)
 

@@ -294,7 +294,7 @@ def test_each_mechanism_alone_as_a_one_layer_model(which, dtype, tmp_path):
     reqs = {"a": helpers.random_tokens(150, cfg["vocab"], 1), "b": helpers.random_tokens(9, cfg["vocab"], 2)}
     tensors = helpers.read_tensors(folder)
     ref = {rid: pp.forward(cfg, tensors, toks).float() for rid, toks in reqs.items()}
-    for steps in (helpers.trace_whole(reqs), helpers.trace_chunks(reqs)):
+    for steps in (helpers.trace_whole(reqs), helpers.trace_chunks(reqs), helpers.trace_decode_tail(reqs, 8)):
         runner = _runner(folder, dtype, 64, helpers.trace_max_tokens(steps, 64))
         _check(helpers.run_trace_with_runner(runner, steps), ref, TOL[dtype])
 
