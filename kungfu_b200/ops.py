@@ -53,6 +53,23 @@ def library():
     return _lib
 
 
+class plain_launches:
+    """Within this context kernels are launched WITHOUT programmatic dependent launch: each starts only when everything
+    before it in the stream has finished.  Needed around a kernel that reads, before its own dependency wait, memory that
+    another kernel of the same step wrote: the decode attention kernels request the step's positions that early, which is
+    safe for the integers the host copied in and not for integers a kernel derived from them."""
+
+    def __enter__(self):
+        if _override is None:
+            library().kf_set_pdl(0)
+        return self
+
+    def __exit__(self, *exc):
+        if _override is None:
+            library().kf_set_pdl(0 if os.environ.get("KUNGFU_PDL", "1") == "0" else 1)
+        return False
+
+
 def library_path() -> str:
     from .csrc import build as _build
     return os.path.join(_build.build_dir(), _build.LIB_NAME)

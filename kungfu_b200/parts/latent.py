@@ -93,8 +93,10 @@ class LatentAttention(Mixer):
         o = ctx.buf("attn_o", (T, H * D), ctx.act_dtype)
         parts = _decode_parts(H) if (H > 16 and getattr(ctx, "decode_only", False)) else 1
         if parts > 1 and H // parts >= 4:
-            ops.paged_attention(q.view(T * parts, (H // parts) * D), o.view(T * parts, (H // parts) * D), _RowsAsParts(ctx, parts),
-                                cache, H // parts, 1, D, self.scale, 0.0, self.window)
+            rows = _RowsAsParts(ctx, parts)
+            with ops.plain_launches():                     # the kernel reads positions early; here a kernel wrote them
+                ops.paged_attention(q.view(T * parts, (H // parts) * D), o.view(T * parts, (H // parts) * D), rows,
+                                    cache, H // parts, 1, D, self.scale, 0.0, self.window)
         else:
             ops.paged_attention(q, o, ctx, cache, H, 1, D, self.scale, 0.0, self.window)
         v = ctx.buf("latent_v", (T, H * self.vdim), ctx.act_dtype)
