@@ -73,8 +73,15 @@ PX_E = config(512, 3000, [layer("latent_attention", latent(4, 64, 64, 128, 0.11)
                           layer("channel_delta", delta(4, 4, 128, 64, 4), dense(1024)),
                           layer("latent_attention", latent(8, 32, 32, 64, 0.15), moe(16, 2, 128, 4.0, 1.0))], scale=3.0, side=16)
 
-CASES = {"A": (PX_A, [5, 17, 23, 40, 11, 30], 4), "B": (PX_B, [1, 31, 40, 70, 9, 50], 8), "C": (PX_C, [3, 50, 64, 29, 77, 2], 16)}
-RANKS = {"A": (5, 7), "B": (12, 6), "C": (9, 9), "E": (32, 24)}          # (decay rank, gate rank) of the channel_delta layers
+# the smallest of everything, and rows that are no multiple of 8 bytes: width 90, vocabulary 101, a latent of 9, keys of 6 and
+# 10, values of 5 and 6, a side input of 3, four experts of which two are taken
+PX_D = config(90, 101, [layer("latent_attention", latent(3, 10, 6, 9, 0.4), moe(4, 2, 18, 1.0, 1.0, shared=(10, 1.0))),
+                        layer("delta", delta(2, 1, 6, 5, 3), dense(34)),
+                        layer("channel_delta", delta(2, 2, 10, 6, 2))], scale=1.0, side=3)
+
+CASES = {"A": (PX_A, [5, 17, 23, 40, 11, 30], 4), "B": (PX_B, [1, 31, 40, 70, 9, 50], 8), "C": (PX_C, [3, 50, 64, 29, 77, 2], 16),
+         "D": (PX_D, [4, 19, 1, 33, 8, 12], 4)}
+RANKS = {"A": (5, 7), "B": (12, 6), "C": (9, 9), "D": (3, 2), "E": (32, 24)}          # (decay rank, gate rank) of the channel_delta layers
 
 
 def draw_tensors(cfg_dict: dict, seed: int, sharp: bool = False, ranks=(6, 10)) -> dict:

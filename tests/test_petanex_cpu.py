@@ -81,7 +81,7 @@ def test_weights_bind_by_name_ranks_come_from_shapes_and_faults_are_listed_toget
     assert "l1.mix.uk" in e.value.missing or any(n == "l0.mix.b" for n, _, _ in e.value.wrong_shape)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "chunks", "mixed"])
 def test_host_logic_on_the_cpu_stand_in(name, mode, tmp_path, cpu_ops):
     cfg, lengths, page = px.CASES[name]

@@ -319,7 +319,7 @@ def _steps(mode, reqs):
             "chunks": helpers.trace_chunks, "mixed": lambda r: helpers.trace_mixed(r, seed=5)}[mode](reqs)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "chunks", "mixed"])
 @pytest.mark.parametrize("dtype,sharp", [("float32", True), ("bfloat16", False)])
 def test_modes_match_plain(models, name, mode, dtype, sharp):
