@@ -119,8 +119,8 @@ __global__ void __launch_bounds__(256) grouped_simt_kernel(KfGroupedArgs p) {
 // a block of eight warps owns 64 rows x 128 weight rows (gated: 64 gate rows and the 64 up rows of the same features, so
 // that the warp that holds a gate value also holds its up value and the activation needs no exchange), K in slices of 32
 // through a ring of three stages filled by 16-byte cp.async copies (32-bit rows are converted on their way into shared
-// memory instead).  Shared rows are 40 elements apart: the eight rows and four column pairs a fragment load touches fall
-// into 32 different banks.  A row's sums do not depend on the other rows of its tile.
+// memory instead).  Shared rows are 40 elements (80 bytes) apart: the eight 16-byte rows of an ldmatrix fall into
+// different banks.  A row's sums do not depend on the other rows of its tile.
 constexpr int TM = 64, TN = 128, TK = 32, TSTAGES = 3, TLD = TK + 8;
 
 template <typename TX, typename TO, int GATED>
@@ -198,20 +198,19 @@ __global__ void __launch_bounds__(256) grouped_mma_kernel(KfGroupedArgs p) {
     const int s = kt % TSTAGES;
 #pragma unroll
     for (int kk = 0; kk < TK; kk += 16) {
+      // fragments by ldmatrix: lane i names row i % 8 of 8 x 8 matrix i / 8.  A: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7),
+      // (rows 0-7, k 8-15), (rows 8-15, k 8-15) are a0..a3; B from [n][k] rows: (n 0-7, k 0-7), (n 0-7, k 8-15) are b0, b1 of
+      // one n-tile and (n 8-15, ...) those of the next.
       uint32_t a[2][4], b[4][2];
+      const int lm = lane >> 3, lr = lane & 7;
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi) {
-        const __nv_bfloat16* base = &xs[s][wm * 32 + mi * 16 + gid][kk + 2 * tig];
-        a[mi][0] = *reinterpret_cast<const uint32_t*>(base);
-        a[mi][1] = *reinterpret_cast<const uint32_t*>(base + 8 * TLD);
-        a[mi][2] = *reinterpret_cast<const uint32_t*>(base + 8);
-        a[mi][3] = *reinterpret_cast<const uint32_t*>(base + 8 * TLD + 8);
-      }
+      for (int mi = 0; mi < 2; ++mi)
+        ldmatrix_x4(a[mi], &xs[s][wm * 32 + mi * 16 + (lm & 1) * 8 + lr][kk + (lm >> 1) * 8]);
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        const __nv_bfloat16* base = &ws[s][wrow_of[nt] + gid][kk + 2 * tig];
-        b[nt][0] = *reinterpret_cast<const uint32_t*>(base);
-        b[nt][1] = *reinterpret_cast<const uint32_t*>(base + 8);
+      for (int np = 0; np < 2; ++np) {
+        uint32_t r[4];
+        ldmatrix_x4(r, &ws[s][wrow_of[2 * np] + (lm >> 1) * 8 + lr][kk + (lm & 1) * 8]);
+        b[2 * np][0] = r[0]; b[2 * np][1] = r[1]; b[2 * np + 1][0] = r[2]; b[2 * np + 1][1] = r[3];
       }
 #pragma unroll
       for (int mi = 0; mi < 2; ++mi)
