@@ -14,8 +14,9 @@
 // is computed once per (row, head), side by side over the whole step, and left laid out as the walk stages it.
 // The walk: a block of 128 threads owns (request, head, 128 / LANES value columns).  Thread (c, l) keeps rows
 // l*NR .. l*NR+NR-1 of column c in registers (d <= LANES * NR; rows beyond d are zero and stay zero); the LANES lanes of
-// a column add their shares of S^T k by shuffles (the one reduction on the chain from token to token), each from two
-// interleaved partial sums so that a chain of dependent multiply-adds is NR / 2 long; their shares of S^T q go to shared
+// a column add their shares of S^T k by shuffles (the one reduction on the chain from token to token), each from four
+// interleaved partial sums held as two pairs that packed instructions (fma.rn.f32x2) update, as they update pairs of
+// neighbouring rows of S; their shares of S^T q go to shared
 // memory and are summed, in a fixed order, after the walk over the stage.  Rows of R tokens at a time arrive in shared
 // memory by 16-byte cp.async copies into one of two stages while the stage before is walked, so that the serial walk is
 // multiply-adds and shared loads only.  A lane's chunk of a staged row starts every LS floats (NR + 4; NR where that is
@@ -118,12 +119,13 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(KfDeltaArgs p, cons
   const int col0 = blockIdx.y * CB, col = col0 + c;
   const bool col_ok = col < p.dv;
   const int d = p.d, dv = p.dv;
-  float S[NR];
+  float2 S[NR / 2];                              // rows l*NR + 2j and + 2j + 1: one packed instruction updates both
   float* sp = p.state + ((size_t)slot * p.H + h) * d * dv;
 #pragma unroll
-  for (int i = 0; i < NR; ++i) {
-    const int r = l * NR + i;
-    S[i] = (r < d && col_ok) ? sp[(size_t)r * dv + col] : 0.f;
+  for (int j = 0; j < NR / 2; ++j) {
+    const int r = l * NR + 2 * j;
+    S[j].x = (r < d && col_ok) ? sp[(size_t)r * dv + col] : 0.f;
+    S[j].y = (r + 1 < d && col_ok) ? sp[(size_t)(r + 1) * dv + col] : 0.f;
   }
 
   // rows t0 .. t0 + nr - 1 of the request into stage `buf` (asynchronous copies, 16 bytes where the source allows)
@@ -168,50 +170,58 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(KfDeltaArgs p, cons
     for (int tt = 0; tt < nr; ++tt) {              // the walk
       const float* kq = &k_s[buf][tt][l * LS];
       const float* qq = &q_s[buf][tt][l * LS];
-      float kr[NR];
-      float kva = 0.f, kvb = 0.f;
+      float2 kr[NR / 2];
+      float2 kva = make_float2(0.f, 0.f), kvb = make_float2(0.f, 0.f);
       if (p.per_channel) {
         const float* gq = &g_s[buf][tt][l * LS];
 #pragma unroll
         for (int i = 0; i < NR; i += 4) {
           const float4 g4 = *reinterpret_cast<const float4*>(gq + i);
           const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
-          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
-          S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
-          kva = fmaf(S[i], k4.x, kva); kvb = fmaf(S[i + 1], k4.y, kvb); kva = fmaf(S[i + 2], k4.z, kva); kvb = fmaf(S[i + 3], k4.w, kvb);
+          kr[i / 2] = make_float2(k4.x, k4.y); kr[i / 2 + 1] = make_float2(k4.z, k4.w);
+          S[i / 2] = __fmul2_rn(S[i / 2], make_float2(g4.x, g4.y));
+          S[i / 2 + 1] = __fmul2_rn(S[i / 2 + 1], make_float2(g4.z, g4.w));
+          kva = __ffma2_rn(S[i / 2], kr[i / 2], kva);
+          kvb = __ffma2_rn(S[i / 2 + 1], kr[i / 2 + 1], kvb);
         }
       } else {
         const float g = small_s[buf][tt][1];
+        const float2 g2 = make_float2(g, g);
 #pragma unroll
         for (int i = 0; i < NR; i += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kq + i);
-          kr[i] = k4.x; kr[i + 1] = k4.y; kr[i + 2] = k4.z; kr[i + 3] = k4.w;
-          S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-          kva = fmaf(S[i], k4.x, kva); kvb = fmaf(S[i + 1], k4.y, kvb); kva = fmaf(S[i + 2], k4.z, kva); kvb = fmaf(S[i + 3], k4.w, kvb);
+          kr[i / 2] = make_float2(k4.x, k4.y); kr[i / 2 + 1] = make_float2(k4.z, k4.w);
+          S[i / 2] = __fmul2_rn(S[i / 2], g2);
+          S[i / 2 + 1] = __fmul2_rn(S[i / 2 + 1], g2);
+          kva = __ffma2_rn(S[i / 2], kr[i / 2], kva);
+          kvb = __ffma2_rn(S[i / 2 + 1], kr[i / 2 + 1], kvb);
         }
       }
-      float kv = kva + kvb;
+      float kv = (kva.x + kva.y) + (kvb.x + kvb.y);
 #pragma unroll
       for (int o = 1; o < LANES; o <<= 1) kv += __shfl_xor_sync(0xffffffffu, kv, o);
       const float u = small_s[buf][tt][0] * (v_s[buf][tt][c] - kv);
-      float oa = 0.f, ob = 0.f;
+      const float2 u2 = make_float2(u, u);
+      float2 oa = make_float2(0.f, 0.f), ob = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < NR; i += 4) {
         const float4 q4 = *reinterpret_cast<const float4*>(qq + i);
-        S[i] = fmaf(kr[i], u, S[i]); S[i + 1] = fmaf(kr[i + 1], u, S[i + 1]);
-        S[i + 2] = fmaf(kr[i + 2], u, S[i + 2]); S[i + 3] = fmaf(kr[i + 3], u, S[i + 3]);
-        oa = fmaf(S[i], q4.x, oa); ob = fmaf(S[i + 1], q4.y, ob); oa = fmaf(S[i + 2], q4.z, oa); ob = fmaf(S[i + 3], q4.w, ob);
+        S[i / 2] = __ffma2_rn(kr[i / 2], u2, S[i / 2]);
+        S[i / 2 + 1] = __ffma2_rn(kr[i / 2 + 1], u2, S[i / 2 + 1]);
+        oa = __ffma2_rn(S[i / 2], make_float2(q4.x, q4.y), oa);
+        ob = __ffma2_rn(S[i / 2 + 1], make_float2(q4.z, q4.w), ob);
       }
-      o_part[buf][tt][c][l] = oa + ob;            // off the chain from token to token: summed by `finish`
+      o_part[buf][tt][c][l] = (oa.x + oa.y) + (ob.x + ob.y);   // off the chain from token to token: summed by `finish`
     }
   }
   __syncthreads();
   finish((n_chunks - 1) & 1, (n_chunks - 1) * R, n - (n_chunks - 1) * R);
   if (p.writes) {
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-      const int r = l * NR + i;
-      if (r < d && col_ok) sp[(size_t)r * dv + col] = S[i];
+    for (int j = 0; j < NR / 2; ++j) {
+      const int r = l * NR + 2 * j;
+      if (r < d && col_ok) sp[(size_t)r * dv + col] = S[j].x;
+      if (r + 1 < d && col_ok) sp[(size_t)(r + 1) * dv + col] = S[j].y;
     }
   }
 }
