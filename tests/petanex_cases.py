@@ -118,7 +118,7 @@ def draw_tensors(cfg_dict: dict, seed: int, sharp: bool = False, ranks=(6, 10)) 
             x = 4.0 * x / (spec.shape[-1] ** 0.5)
         elif name in ("embed", "side.embed"):
             x = 0.5 * x
-        elif name.endswith("mix.q") and sharp and spec.shape[0] != spec.shape[1] and ".mix.q" in name and _is_latent(cfg, name):
+        elif name.endswith("mix.q") and sharp and _is_latent(cfg, name):
             x = 4.0 * x / (spec.shape[-1] ** 0.5)
         else:
             x = x / (spec.shape[-1] ** 0.5)                  # projections keep the spread of their input
