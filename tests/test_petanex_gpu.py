@@ -444,7 +444,8 @@ def test_generate_through_the_entry_point(models, dtype):
 
 
 def test_programs_in_bin(models, tmp_path):
-    """bin/trace_run replays a trace of a Petanex folder; bin/kungfu inspects the folder and completes a prompt."""
+    """bin/trace_run replays a trace of a Petanex folder; bin/kungfu inspects the folder, completes a prompt, scores a
+    sequence and times the model."""
     folder, cfg, reqs, ref, page = models[("A", True)]
     steps = helpers.trace_mixed(reqs, seed=2)
     out = tmp_path / "out"
@@ -481,3 +482,19 @@ def test_programs_in_bin(models, tmp_path):
         if float(top[0] - top[1]) > 1e-3 * float(logits.abs().max()):
             assert int(torch.argmax(logits)) == tok
         seq.append(tok)
+    # score: the best token at every place, a prefix in one pass and the rest token by token
+    ids = reqs["r3"][:24]
+    p = subprocess.run([sys.executable, kungfu, "score", "--model", folder, "--ids", json.dumps(ids), "--prefix", "9", "--dtype", "float32",
+                        "--ctx", "256"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    pred = json.loads(p.stdout.strip().splitlines()[-1])["predictions"]
+    logits = pp.forward(cfg, tensors, ids)
+    assert len(pred) == len(ids)
+    for i, tok in enumerate(pred):
+        top = torch.topk(logits[i], 2).values
+        if float(top[0] - top[1]) > 1e-3 * float(logits[i].abs().max()):
+            assert int(torch.argmax(logits[i])) == tok
+    p = subprocess.run([sys.executable, kungfu, "bench", "--model", folder, "--pp", "40", "--tg", "6", "--reps", "1", "--ctx", "256"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "| Petanex | bfloat16 | pp40 |" in p.stdout and "| Petanex | bfloat16 | tg6 |" in p.stdout
